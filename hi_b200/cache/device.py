@@ -37,7 +37,7 @@ def bytes_per_token(cache_specs: Dict[int, Optional[CacheSpec]], element_size: i
     out = [0] * len(groups)
     for slot, spec in cache_specs.items():
         if spec is not None and spec.paged:
-            out[group_of[slot]] += 2 * spec.kv_heads * spec.head_dim * element_size
+            out[group_of[slot]] += (2 if spec.values else 1) * spec.kv_heads * spec.head_dim * element_size
     return out
 
 
@@ -84,14 +84,16 @@ class DeviceCache:
         self.views: Dict[int, CacheView] = {}
         self.bytes = 0
         for slot, spec in cache_specs.items():
-            view = CacheView()
+            view = CacheView(slot=slot)
             if spec is not None and spec.paged:
                 g = self.group_of[slot]
                 shape = (pages_per_group[g], spec.kv_heads, page_size, spec.head_dim)
                 view.group = g
                 view.k_pages = torch.zeros(shape, dtype=dtype, device=self.device)
-                view.v_pages = torch.zeros(shape, dtype=dtype, device=self.device)
-                self.bytes += 2 * view.k_pages.numel() * view.k_pages.element_size()
+                self.bytes += view.k_pages.numel() * view.k_pages.element_size()
+                if spec.values:
+                    view.v_pages = torch.zeros(shape, dtype=dtype, device=self.device)
+                    self.bytes += view.v_pages.numel() * view.v_pages.element_size()
             if spec is not None and spec.state_shape:
                 sdt = getattr(torch, spec.state_dtype)
                 view.state = torch.zeros((max_requests, *spec.state_shape), dtype=sdt, device=self.device)
@@ -114,4 +116,5 @@ class DeviceCache:
             if pages:
                 idx = torch.tensor(pages, device=self.device, dtype=torch.long)
                 view.k_pages[idx] = float("nan")
-                view.v_pages[idx] = float("nan")
+                if view.v_pages is not None:
+                    view.v_pages[idx] = float("nan")

@@ -23,6 +23,9 @@ class Architecture:
     # other layouts of the same weights: {normalised name: shape} of the checkpoint -> {part name:
     # DerivedTensor} for tensors that have to be made from others (split, transposed); optional
     derive_tensors: Optional[Callable[[Dict[str, tuple]], Dict[str, Any]]] = None
+    # sizes that config.json does not hold and only the checkpoint's tensor shapes give:
+    # (typed config, {normalised name: shape}) -> typed config; optional
+    sizes_from_tensors: Optional[Callable[[Any, Dict[str, tuple]], Any]] = None
 
 
 _BY_NAME: Dict[str, Architecture] = {}
@@ -56,11 +59,13 @@ def lookup(raw_config: Dict[str, Any]) -> Architecture:
     archs = raw_config.get("architectures") or []
     if isinstance(archs, str):
         archs = [archs]
-    for name in list(archs) + [raw_config.get("model_type")]:
+    # a config may name its one architecture under the singular key
+    for name in list(archs) + [raw_config.get("architecture"), raw_config.get("model_type")]:
         if isinstance(name, str) and name in _BY_NAME:
             return _BY_NAME[name]
     raise ConfigError(
-        f"config.json: no model is registered for architectures {list(archs)!r} / model_type "
+        f"config.json: no model is registered for architectures "
+        f"{list(archs) + ([raw_config['architecture']] if raw_config.get('architecture') else [])!r} / model_type "
         f"{raw_config.get('model_type')!r}; registered: {registered_architectures()}")
 
 
@@ -68,4 +73,19 @@ def load_architecture(model_dir: str):
     """(architecture, typed config, raw config) of a model folder."""
     raw, gen = read_config_files(model_dir)
     arch = lookup(raw)
-    return arch, arch.parse_config(raw, gen), raw
+    cfg = arch.parse_config(raw, gen)
+    if arch.sizes_from_tensors is not None:
+        from ..weights.safetensors_io import Checkpoint, SafetensorsError
+
+        try:
+            ckpt = Checkpoint(model_dir)
+        except SafetensorsError:
+            ckpt = None              # a folder with a config only: the loader will say what is missing
+        if ckpt is not None:
+            shapes = {}
+            for original in ckpt.names():
+                name = arch.normalize_tensor_name(original)
+                if name is not None:
+                    shapes[name] = tuple(ckpt.describe(original)[1])
+            cfg = arch.sizes_from_tensors(cfg, shapes)
+    return arch, cfg, raw

@@ -100,6 +100,38 @@ int hb_ranked_rows(const float* logits, int rows, int vocab, const float* temper
 int hb_argmax_rows(const float* logits, int rows, int vocab, int parts, float* part_val, int* part_idx, int* counters,
                    int* out, cudaStream_t stream);
 
+// gated_block.cu: gated sum of two sub-layer results into the stream, the weighted average of all layer
+// results so far, and up to two Dynamic Tanh norms of it, in one pass; the xIELU activation
+int hb_gated_depth_dyt(const float* x, const void* delta0, int delta0_dtype, const void* gate0, int gate0_dtype,
+                       const void* delta1, int delta1_dtype, const void* gate1, int gate1_dtype, float* hist,
+                       long long hist_stride, int n_prev, const float* mix, float* z_out, const float* alpha0,
+                       const void* w0, const void* b0, void* y0, const float* alpha1, const void* w1, const void* b1,
+                       void* y1, int wb_dtype, int y_dtype, const int* row_map, int rows, int width,
+                       cudaStream_t stream);
+int hb_xielu(const void* in, void* out, int dtype, const float* coef, long long n, cudaStream_t stream);
+
+// latent.cu: RMS-normed latent rows into their pages; a sigmoid gate per (token, head)
+int hb_latent_append(const void* in, int dtype, long long in_stride, const void* w, float eps, const int* positions,
+                     const int* seq_of_token, const int* block_table, int table_stride, void* pages, int page_size,
+                     int rank, int row_len, int n_tokens, cudaStream_t stream);
+int hb_head_gate(const void* in, const void* gate, long long gate_stride, void* out, int dtype, int n_tokens,
+                 int heads, int dim, cudaStream_t stream);
+
+// delta_rule.cu: the gated delta rule with a decay per head and key channel
+int hb_delta_prep(const void* proj, int proj_dtype, long long ld, int chan_off, int beta_off, const float* taps,
+                  float* state, long long state_stride, long long conv_off, const void* a_pre, int a_dtype,
+                  const float* dt_bias, const float* a_log, const int* cu_seqlens, const int* seq_of_token,
+                  const int* slots, float* q, float* k, float* v, float* beta, float* decay, int n_tokens, int heads,
+                  int kvh, int dim, int vdim, int taps_n, cudaStream_t stream);
+int hb_delta_conv_update(const void* proj, int proj_dtype, long long ld, int chan_off, float* state,
+                         long long state_stride, long long conv_off, const int* cu_seqlens, const int* slots,
+                         int n_seqs, int channels, int taps_n, cudaStream_t stream);
+int hb_delta_recurrence(const float* q, const float* k, const float* v, const float* beta, const float* decay,
+                        float* state, long long state_stride, const int* cu_seqlens, const int* slots, float* out,
+                        int n_seqs, int heads, int kvh, int dim, int vdim, int force_general, cudaStream_t stream);
+int hb_delta_out_norm(const float* o, const void* gate, int gate_dtype, const void* w, float eps, void* out, int dtype,
+                      long long rows, int vdim, cudaStream_t stream);
+
 // seeded random weights: out[i] = value of element first + i of the tensor with `key` (random_fill.cu)
 int hb_random_normal(void* out, int dtype, long long n, long long first, unsigned long long key, float scale,
                      cudaStream_t stream);

@@ -1,0 +1,352 @@
+// The gated delta rule with one decay per head and key channel: a recurrent mixer whose per-request
+// state is a matrix S [dim, vdim] per head in float32, plus the last (taps - 1) inputs of the short
+// causal convolutions that q, k and v pass.
+//
+//   delta_prep         per token: convolution over time + silu of the q | k | v channels (the rows before the
+//                      portion's first token come from the request's state), q and k to unit length per head
+//                      (q also times dim^-1/2), beta = sigmoid(.), decay = exp(-exp(A_log) * softplus(a + dt_bias))
+//   delta_conv_update  per request: the last (taps - 1) inputs of the portion replace the state's
+//   delta_recurrence   per (request, head, group of value columns), token after token:
+//                        S <- decay * S (rows);  u = beta * (v - S^T k);  S <- S + k u^T;  o = S^T q
+//                      A thread owns one column of S, so nothing is exchanged between threads but k, q and the
+//                      decay of the token, which the block stages in shared memory one token ahead.
+//   delta_out_norm     o / sqrt(mean_vdim(o^2) + eps) * w * sigmoid(gate)
+//
+// Everything here is float32 arithmetic; only the projections that come in and the normed output that
+// goes out have the engine's dtype. The state of a request depends on its own tokens only and the order of
+// the sums is fixed, so the result does not depend on how the tokens were cut into steps or batched.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float ldf(const void* p, int dtype, size_t i) {
+  return dtype == HB_DTYPE_F32 ? reinterpret_cast<const float*>(p)[i]
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ float sigmoid1(float v) { return 1.f / (1.f + expf(-v)); }
+
+struct PrepArgs {
+  const void* proj;          // [N, ld]: ... q | k | v channels from column `chan_off`, beta from `beta_off`
+  int proj_dtype;
+  long long ld;
+  int chan_off, beta_off;
+  const float* taps;         // [C, K]
+  float* state;              // [slots, state_stride]
+  long long state_stride, conv_off;
+  const void* a_pre;         // [N, heads * dim]
+  int a_dtype;
+  const float* dt_bias;      // [heads * dim]
+  const float* a_log;        // [heads]
+  const int* cu_seqlens;
+  const int* seq_of_token;
+  const int* slots;
+  float* q;                  // [N, kvh * dim]
+  float* k;                  // [N, kvh * dim]
+  float* v;                  // [N, heads * vdim]
+  float* beta;               // [N, heads]
+  float* decay;              // [N, heads * dim]
+  int heads, kvh, dim, vdim, K;
+};
+
+__global__ void delta_prep_kernel(const PrepArgs a) {
+  extern __shared__ float y[];     // C values after convolution and silu
+  const int t = blockIdx.x;
+  const int s = a.seq_of_token[t];
+  const int start = a.cu_seqlens[s];
+  const int local = t - start;
+  const int qk = a.kvh * a.dim, C = 2 * qk + a.heads * a.vdim, K = a.K;
+  const float* conv = a.state + (size_t)a.slots[s] * a.state_stride + a.conv_off;   // [K-1, C]
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < K; ++j) {
+      const int rel = local - (K - 1) + j;
+      const float x = rel >= 0 ? ldf(a.proj, a.proj_dtype, (size_t)(start + rel) * a.ld + a.chan_off + c)
+                               : conv[(size_t)(K - 1 + rel) * C + c];
+      acc += a.taps[(size_t)c * K + j] * x;
+    }
+    y[c] = acc * sigmoid1(acc);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const float qscale = 1.f / sqrtf((float)a.dim);
+  for (int g = warp; g < 2 * a.kvh; g += nwarps) {
+    const float* src = y + (size_t)g * a.dim;
+    float ss = 0.f;
+    for (int i = lane; i < a.dim; i += 32) ss += src[i] * src[i];
+    ss = hb::warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss + 1e-6f);
+    const bool is_q = g < a.kvh;
+    float* dst = is_q ? a.q + (size_t)t * qk + (size_t)g * a.dim : a.k + (size_t)t * qk + (size_t)(g - a.kvh) * a.dim;
+    for (int i = lane; i < a.dim; i += 32) dst[i] = is_q ? src[i] * inv * qscale : src[i] * inv;
+  }
+  const int HV = a.heads * a.vdim, HD = a.heads * a.dim;
+  for (int i = threadIdx.x; i < HV; i += blockDim.x) a.v[(size_t)t * HV + i] = y[2 * qk + i];
+  for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+    a.beta[(size_t)t * a.heads + h] = sigmoid1(ldf(a.proj, a.proj_dtype, (size_t)t * a.ld + a.beta_off + h));
+  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+    const float x = ldf(a.a_pre, a.a_dtype, (size_t)t * HD + i) + a.dt_bias[i];
+    const float sp = x > 20.f ? x : log1pf(expf(x));
+    a.decay[(size_t)t * HD + i] = expf(-expf(a.a_log[i / a.dim]) * sp);
+  }
+}
+
+__global__ void delta_conv_update_kernel(const void* proj, int proj_dtype, long long ld, int chan_off, float* state,
+                                         long long state_stride, long long conv_off, const int* cu_seqlens,
+                                         const int* slots, int C, int K) {
+  const int s = blockIdx.x;
+  const int start = cu_seqlens[s], n = cu_seqlens[s + 1] - start;
+  if (n <= 0) return;
+  float* conv = state + (size_t)slots[s] * state_stride + conv_off;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    // row i of the new state is input (n - (K-1) + i) of the portion; a negative one is row (n + i) of the
+    // old state, which lies behind every row written so far
+    for (int i = 0; i < K - 1; ++i) {
+      const int rel = n - (K - 1) + i;
+      conv[(size_t)i * C + c] = rel >= 0 ? ldf(proj, proj_dtype, (size_t)(start + rel) * ld + chan_off + c)
+                                         : conv[(size_t)(n + i) * C + c];
+    }
+  }
+}
+
+struct RecurArgs {
+  const float* q;       // [N, kvh * dim]
+  const float* k;
+  const float* v;       // [N, heads * vdim]
+  const float* beta;    // [N, heads]
+  const float* decay;   // [N, heads * dim]
+  float* state;         // [slots, state_stride], S of head h at h * dim * vdim, row-major [dim, vdim]
+  long long state_stride;
+  const int* cu_seqlens;
+  const int* slots;
+  float* out;           // [N, heads * vdim]
+  int heads, kvh, dim, vdim;
+};
+
+// Stage token t's k, q and decay rows (dim floats each) into buf[0..3*DIMP): k, q, g.
+__device__ __forceinline__ void stage_token(const RecurArgs& a, int t, int head, int kvhead, float* buf, int dimp) {
+  for (int i = threadIdx.x; i < dimp; i += blockDim.x) {
+    const bool in = i < a.dim;
+    buf[i] = in ? a.k[(size_t)t * a.kvh * a.dim + (size_t)kvhead * a.dim + i] : 0.f;
+    buf[dimp + i] = in ? a.q[(size_t)t * a.kvh * a.dim + (size_t)kvhead * a.dim + i] : 0.f;
+    buf[2 * dimp + i] = in ? a.decay[(size_t)t * a.heads * a.dim + (size_t)head * a.dim + i] : 1.f;
+  }
+}
+
+// A column of S in the registers of SPLIT lanes of one warp, 32 rows each: lane = part * (32 / SPLIT) + c
+// holds rows r * SPLIT + part (r < 32) of the warp's column c; rows beyond dim stay zero. dim <= 32 * SPLIT.
+// The two dot products of a token are summed within a thread in four interleaved chains, then across
+// the SPLIT lanes by a butterfly: the order is fixed.
+template <int SPLIT>
+__global__ void __launch_bounds__(64) delta_recurrence_reg_kernel(const RecurArgs a) {
+  constexpr int DIMP = 32 * SPLIT, WCOLS = 32 / SPLIT;
+  __shared__ float stage[2][3 * DIMP];
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = lane / WCOLS;
+  const int col = (blockIdx.x * (blockDim.x >> 5) + warp) * WCOLS + (lane % WCOLS);
+  const bool active = col < a.vdim;
+  const int kvhead = head / (a.heads / a.kvh);
+  const int first = a.cu_seqlens[seq], last = a.cu_seqlens[seq + 1];
+  if (first >= last) return;
+  float* S = a.state + (size_t)a.slots[seq] * a.state_stride + (size_t)head * a.dim * a.vdim;
+  float s[32];
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const int i = r * SPLIT + part;
+    s[r] = (active && i < a.dim) ? S[(size_t)i * a.vdim + col] : 0.f;
+  }
+  stage_token(a, first, head, kvhead, stage[0], DIMP);
+  __syncthreads();
+  for (int t = first; t < last; ++t) {
+    const float* cur = stage[(t - first) & 1] + part;
+    if (t + 1 < last) stage_token(a, t + 1, head, kvhead, stage[(t - first + 1) & 1], DIMP);
+    const float vj = active ? a.v[(size_t)t * a.heads * a.vdim + (size_t)head * a.vdim + col] : 0.f;
+    const float bt = a.beta[(size_t)t * a.heads + head];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      s[r] *= cur[2 * DIMP + r * SPLIT];
+      acc[r & 3] = fmaf(s[r], cur[r * SPLIT], acc[r & 3]);
+    }
+    float dot = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+    for (int o = WCOLS; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float u = bt * (vj - dot);
+    float oa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      s[r] = fmaf(cur[r * SPLIT], u, s[r]);
+      oa[r & 3] = fmaf(s[r], cur[DIMP + r * SPLIT], oa[r & 3]);
+    }
+    float out = (oa[0] + oa[1]) + (oa[2] + oa[3]);
+#pragma unroll
+    for (int o = WCOLS; o < 32; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+    if (active && part == 0) a.out[(size_t)t * a.heads * a.vdim + (size_t)head * a.vdim + col] = out;
+    __syncthreads();
+  }
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      const int i = r * SPLIT + part;
+      if (i < a.dim) S[(size_t)i * a.vdim + col] = s[r];
+    }
+  }
+}
+
+// Any dim: the block's columns of S in shared memory, [dim][blockDim.x].
+__global__ void delta_recurrence_smem_kernel(const RecurArgs a) {
+  extern __shared__ float smem[];
+  const int dim = a.dim, cols = blockDim.x;
+  float* stage0 = smem;                 // [2][3 * dim]
+  float* sm = smem + 6 * (size_t)dim;   // [dim][cols]
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int col = blockIdx.x * cols + threadIdx.x;
+  const bool active = col < a.vdim;
+  const int kvhead = head / (a.heads / a.kvh);
+  const int first = a.cu_seqlens[seq], last = a.cu_seqlens[seq + 1];
+  if (first >= last) return;
+  float* S = a.state + (size_t)a.slots[seq] * a.state_stride + (size_t)head * dim * a.vdim;
+  float* mine = sm + threadIdx.x;
+  for (int i = 0; i < dim; ++i) mine[(size_t)i * cols] = active ? S[(size_t)i * a.vdim + col] : 0.f;
+  stage_token(a, first, head, kvhead, stage0, dim);
+  __syncthreads();
+  for (int t = first; t < last; ++t) {
+    const float* cur = stage0 + (size_t)((t - first) & 1) * 3 * dim;
+    if (t + 1 < last) stage_token(a, t + 1, head, kvhead, stage0 + (size_t)((t - first + 1) & 1) * 3 * dim, dim);
+    const float vj = active ? a.v[(size_t)t * a.heads * a.vdim + (size_t)head * a.vdim + col] : 0.f;
+    const float bt = a.beta[(size_t)t * a.heads + head];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < dim; ++i) {
+      const float si = mine[(size_t)i * cols] * cur[2 * dim + i];
+      mine[(size_t)i * cols] = si;
+      acc[i & 3] = fmaf(si, cur[i], acc[i & 3]);
+    }
+    const float u = bt * (vj - ((acc[0] + acc[1]) + (acc[2] + acc[3])));
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < dim; ++i) {
+      const float si = fmaf(cur[i], u, mine[(size_t)i * cols]);
+      mine[(size_t)i * cols] = si;
+      o[i & 3] = fmaf(si, cur[dim + i], o[i & 3]);
+    }
+    if (active) a.out[(size_t)t * a.heads * a.vdim + (size_t)head * a.vdim + col] = (o[0] + o[1]) + (o[2] + o[3]);
+    __syncthreads();
+  }
+  if (active)
+    for (int i = 0; i < dim; ++i) S[(size_t)i * a.vdim + col] = mine[(size_t)i * cols];
+}
+
+// One warp per (token, head).
+template <typename T>
+__global__ void delta_out_norm_kernel(const float* __restrict__ o, const void* __restrict__ gate, int gate_dtype,
+                                      const T* __restrict__ w, float eps, T* __restrict__ out, long long rows,
+                                      int vdim) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* src = o + row * vdim;
+  float ss = 0.f;
+  for (int j = lane; j < vdim; j += 32) ss += src[j] * src[j];
+  const float inv = 1.f / sqrtf(hb::warp_sum(ss) / (float)vdim + eps);
+  for (int j = lane; j < vdim; j += 32) {
+    const float g = sigmoid1(ldf(gate, gate_dtype, (size_t)row * vdim + j));
+    out[row * vdim + j] = hb::from_f32<T>(src[j] * inv * hb::to_f32(w[j]) * g);
+  }
+}
+
+}  // namespace
+
+extern "C" int hb_delta_prep(const void* proj, int proj_dtype, long long ld, int chan_off, int beta_off,
+                             const float* taps, float* state, long long state_stride, long long conv_off,
+                             const void* a_pre, int a_dtype, const float* dt_bias, const float* a_log,
+                             const int* cu_seqlens, const int* seq_of_token, const int* slots, float* q, float* k,
+                             float* v, float* beta, float* decay, int n_tokens, int heads, int kvh, int dim, int vdim,
+                             int taps_n, cudaStream_t stream) {
+  if (!proj || !taps || !state || !a_pre || !dt_bias || !a_log || !cu_seqlens || !seq_of_token || !slots || !q || !k ||
+      !v || !beta || !decay)
+    return HB_ERR_BAD_ARG;
+  if (heads <= 0 || kvh <= 0 || heads % kvh || dim <= 0 || vdim <= 0 || taps_n < 1 || n_tokens < 0) return HB_ERR_BAD_ARG;
+  if (n_tokens == 0) return HB_OK;
+  const size_t C = 2 * (size_t)kvh * dim + (size_t)heads * vdim;
+  const size_t smem = C * sizeof(float);
+  if (smem > 200 * 1024) return HB_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  PrepArgs a;
+  a.proj = proj; a.proj_dtype = proj_dtype; a.ld = ld; a.chan_off = chan_off; a.beta_off = beta_off; a.taps = taps;
+  a.state = state; a.state_stride = state_stride; a.conv_off = conv_off; a.a_pre = a_pre; a.a_dtype = a_dtype;
+  a.dt_bias = dt_bias; a.a_log = a_log; a.cu_seqlens = cu_seqlens; a.seq_of_token = seq_of_token; a.slots = slots;
+  a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay;
+  a.heads = heads; a.kvh = kvh; a.dim = dim; a.vdim = vdim; a.K = taps_n;
+  delta_prep_kernel<<<n_tokens, C >= 1024 ? 256 : 128, smem, stream>>>(a);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_delta_conv_update(const void* proj, int proj_dtype, long long ld, int chan_off, float* state,
+                                    long long state_stride, long long conv_off, const int* cu_seqlens,
+                                    const int* slots, int n_seqs, int channels, int taps_n, cudaStream_t stream) {
+  if (!proj || !state || !cu_seqlens || !slots || channels <= 0 || taps_n < 1 || n_seqs < 0) return HB_ERR_BAD_ARG;
+  if (n_seqs == 0 || taps_n == 1) return HB_OK;
+  int per = (channels + 127) / 128;
+  if (per > 16) per = 16;
+  delta_conv_update_kernel<<<dim3(n_seqs, per), 128, 0, stream>>>(proj, proj_dtype, ld, chan_off, state, state_stride,
+                                                                  conv_off, cu_seqlens, slots, channels, taps_n);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_delta_recurrence(const float* q, const float* k, const float* v, const float* beta,
+                                   const float* decay, float* state, long long state_stride, const int* cu_seqlens,
+                                   const int* slots, float* out, int n_seqs, int heads, int kvh, int dim, int vdim,
+                                   int force_general, cudaStream_t stream) {
+  if (!q || !k || !v || !beta || !decay || !state || !cu_seqlens || !slots || !out) return HB_ERR_BAD_ARG;
+  if (heads <= 0 || kvh <= 0 || heads % kvh || dim <= 0 || vdim <= 0 || n_seqs < 0) return HB_ERR_BAD_ARG;
+  if (n_seqs == 0) return HB_OK;
+  RecurArgs a;
+  a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay; a.state = state; a.state_stride = state_stride;
+  a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.heads = heads; a.kvh = kvh; a.dim = dim; a.vdim = vdim;
+  if (!force_general && dim <= 256) {
+    const int split = dim <= 32 ? 1 : (dim <= 64 ? 2 : (dim <= 128 ? 4 : 8));
+    const int cols = 2 * (32 / split);      // two warps a block
+    dim3 grid((vdim + cols - 1) / cols, heads, n_seqs);
+    if (split == 1) delta_recurrence_reg_kernel<1><<<grid, 64, 0, stream>>>(a);
+    else if (split == 2) delta_recurrence_reg_kernel<2><<<grid, 64, 0, stream>>>(a);
+    else if (split == 4) delta_recurrence_reg_kernel<4><<<grid, 64, 0, stream>>>(a);
+    else delta_recurrence_reg_kernel<8><<<grid, 64, 0, stream>>>(a);
+  } else {
+    const int cols = vdim > 32 ? 64 : 32;
+    dim3 grid((vdim + cols - 1) / cols, heads, n_seqs);
+    const size_t smem = ((size_t)6 * dim + (size_t)dim * cols) * sizeof(float);
+    if (smem > 200 * 1024) return HB_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(delta_recurrence_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    delta_recurrence_smem_kernel<<<grid, cols, smem, stream>>>(a);
+  }
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_delta_out_norm(const float* o, const void* gate, int gate_dtype, const void* w, float eps, void* out,
+                                 int dtype, long long rows, int vdim, cudaStream_t stream) {
+  if (!o || !gate || !w || !out || rows < 0 || vdim <= 0) return HB_ERR_BAD_ARG;
+  if (rows == 0) return HB_OK;
+  const int warps = 4;
+  const long long blocks = (rows + warps - 1) / warps;
+  if (blocks > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
+  if (dtype == HB_DTYPE_F32)
+    delta_out_norm_kernel<float><<<(int)blocks, warps * 32, 0, stream>>>(o, gate, gate_dtype, (const float*)w, eps,
+                                                                         (float*)out, rows, vdim);
+  else if (dtype == HB_DTYPE_BF16)
+    delta_out_norm_kernel<__nv_bfloat16><<<(int)blocks, warps * 32, 0, stream>>>(
+        o, gate, gate_dtype, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out, rows, vdim);
+  else
+    return HB_ERR_BAD_ARG;
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}

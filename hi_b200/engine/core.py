@@ -457,11 +457,17 @@ class _DecodeGraph:
         # valid inputs for the capture run: the tokens fed on the device included
         eng._build_context(entries, widths=self.widths, static=self, feedback=feedback)
         torch.cuda.synchronize()
+        # The run outside the capture executes the step, and so does the first replay. Appending a token's
+        # keys twice writes the same rows twice; advancing a recurrent mixer's state twice does not give
+        # the same state, so the requests' fixed-size states are put back after the run.
+        states = [(view.state, view.state.clone()) for view in eng.cache.views.values() if view.state is not None]
         stream = torch.cuda.Stream()
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):                                   # once outside capture, on a side stream
             eng.model.forward(self.ctx, eng.cache.views, self.logit_rows)
         torch.cuda.current_stream().wait_stream(stream)
+        for state, before in states:
+            state.copy_(before)
         torch.cuda.synchronize()
         before = ops.LAUNCHES[0]
         ops.TC_USED[0] = False

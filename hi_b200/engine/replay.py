@@ -84,7 +84,8 @@ def run(args, stdin=None, stdout=None) -> int:
         step = obj["step"]
         entries = [StepEntry(e["id"], e["tokens"], e.get("want", [])) for e in obj.get("entries", [])]
         taps = {}
-        tap = (lambda name, t: taps.__setitem__(name, t.detach().to("cpu").tolist())) if args.dump_taps else None
+        tap = (lambda name, t: None if t.is_floating_point() else taps.__setitem__(name, t.detach().to("cpu").tolist())) \
+            if args.dump_taps else None
         logits = engine.step(entries, tap=tap) if entries else None
         if args.dump_taps:
             with open(os.path.join(args.out, f"{step}.taps.json"), "w") as f:

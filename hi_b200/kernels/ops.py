@@ -43,6 +43,15 @@ _SIGNATURES = {
     "hb_sample_rows": [P, I, I, P, P, P, P],
     "hb_sample_rows_parts": [P, I, I, I, P, P, P, P, P, P, P, P, P],
     "hb_random_normal": [P, I, c_longlong, c_longlong, c_uint64, F, P],
+    "hb_gated_depth_dyt": [P, P, I, P, I, P, I, P, I, P, c_longlong, I, P, P, P, P, P, P, P, P, P, P, I, I, P, I, I, P],
+    "hb_xielu": [P, P, I, P, c_longlong, P],
+    "hb_latent_append": [P, I, c_longlong, P, F, P, P, P, I, P, I, I, I, I, P],
+    "hb_head_gate": [P, P, c_longlong, P, I, I, I, I, P],
+    "hb_delta_prep": [P, I, c_longlong, I, I, P, P, c_longlong, c_longlong, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I,
+                      I, I, I, P],
+    "hb_delta_conv_update": [P, I, c_longlong, I, P, c_longlong, c_longlong, P, P, I, I, I, P],
+    "hb_delta_recurrence": [P, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, I, P],
+    "hb_delta_out_norm": [P, P, I, P, F, P, I, c_longlong, I, P],
 }
 
 _UNSUPPORTED = 1002
@@ -118,11 +127,17 @@ def feed_tokens(tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, samp
     _check(lib().hb_feed_tokens(_ptr(tokens), _ptr(dst), _ptr(src), _ptr(sampled), dst.numel(), _stream()), "feed_tokens")
 
 
-def embed_gather(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
-    """Rows of ``table`` [V, H] for int32 ``tokens`` [N] -> float32 residual stream [N, H]."""
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows of ``table`` [V, H] for int32 ``tokens`` [N] -> float32 residual stream [N, H] (into ``out``
+    if given)."""
     _need(table, "table"); _need(tokens, "tokens", torch.int32)
     n, (vocab, hidden) = tokens.numel(), table.shape
-    out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    else:
+        _need(out, "out", torch.float32)
+        if tuple(out.shape) != (n, hidden):
+            raise KernelError(f"out has shape {tuple(out.shape)}, expected {(n, hidden)}")
     _check(lib().hb_embed_gather(_ptr(table), _dt(table), _ptr(tokens), _ptr(out), n, hidden, vocab, _stream()),
            "embed_gather")
     return out
@@ -189,6 +204,202 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
         raise KernelError("swiglu input needs an even number of columns")
     out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _check(lib().hb_swiglu(_ptr(gate_up), _ptr(out), _dt(gate_up), n, two_i // 2, _stream()), "swiglu")
+    return out
+
+
+# --------------------------------------------------------------------------- gated parallel block
+def gated_depth_dyt(x: torch.Tensor, terms, history: Optional[torch.Tensor], n_prev: int,
+                    mix: Optional[torch.Tensor], norms, out_dtype: torch.dtype,
+                    row_map: Optional[torch.Tensor] = None, want_z: bool = True):
+    """One pass over the rows of the float32 stream ``x`` [N, W]:
+
+        s = x + sum_k sigmoid(gate_k) * delta_k      ``terms``: up to two (delta, gate | None), [N, W] each
+        history[n_prev] = s                          ``history`` float32 [entries, N, W] (None: not kept)
+        z = sum_{j <= n_prev} mix[j] * history[j]    ``mix`` float32 [n_prev + 1] (None: z = s)
+        y_k = tanh(alpha_k z) w_k + b_k              ``norms``: up to two (alpha float32 [1], w [W], b [W])
+
+    Returns ``(z | None, [y_k])``; ``y_k`` in ``out_dtype``. With ``row_map`` (int32 [R]) only those rows are
+    worked out (outputs [R, W]) and the history is read but not extended."""
+    _need(x, "x", torch.float32)
+    n, width = x.shape
+    terms = list(terms) + [(None, None)] * (2 - len(terms))
+    norms = list(norms) + [None] * (2 - len(norms))
+    if len(terms) > 2 or len(norms) > 2:
+        raise KernelError("at most two gated terms and two norms")
+    for d, g in terms:
+        for t, nm in ((d, "delta"), (g, "gate")):
+            if t is not None:
+                _need(t, nm)
+                if tuple(t.shape) != (n, width):
+                    raise KernelError(f"{nm} has shape {tuple(t.shape)}, the stream {(n, width)}")
+        if d is None and g is not None:
+            raise KernelError("a gate without its term")
+    if history is not None:
+        _need(history, "history", torch.float32)
+        if history.dim() != 3 or tuple(history.shape[1:]) != (n, width) or not 0 <= n_prev < history.shape[0]:
+            raise KernelError(f"history {tuple(history.shape)} does not take entry {n_prev} of a {(n, width)} stream")
+    if mix is not None:
+        _need(mix, "mix", torch.float32)
+        if history is None or mix.numel() != n_prev + 1:
+            raise KernelError(f"mix has {mix.numel()} weights for {n_prev + 1} results")
+    rows = n
+    if row_map is not None:
+        _need(row_map, "row_map", torch.int32)
+        rows = row_map.numel()
+    wb_dtype = None
+    for nrm in norms:
+        if nrm is None:
+            continue
+        alpha, w, b = nrm
+        _need(alpha, "alpha", torch.float32); _need(w, "norm weight"); _need(b, "norm bias", w.dtype)
+        if w.numel() != width or b.numel() != width or alpha.numel() != 1:
+            raise KernelError("norm tensors do not match the stream's width")
+        if wb_dtype is not None and w.dtype != wb_dtype:
+            raise KernelError("the two norms need one dtype")
+        wb_dtype = w.dtype
+    z = torch.empty((rows, width), dtype=torch.float32, device=x.device) if want_z else None
+    ys = [None if nrm is None else torch.empty((rows, width), dtype=out_dtype, device=x.device) for nrm in norms]
+    dt = lambda t: 0 if t is None else _dt(t)
+    (d0, g0), (d1, g1) = terms
+    a = [(None, None, None) if nrm is None else nrm for nrm in norms]
+    _check(lib().hb_gated_depth_dyt(
+        _ptr(x), _ptr(d0), dt(d0), _ptr(g0), dt(g0), _ptr(d1), dt(d1), _ptr(g1), dt(g1),
+        _ptr(history), n * width, int(n_prev), _ptr(mix), _ptr(z),
+        _ptr(a[0][0]), _ptr(a[0][1]), _ptr(a[0][2]), _ptr(ys[0]), _ptr(a[1][0]), _ptr(a[1][1]), _ptr(a[1][2]), _ptr(ys[1]),
+        0 if wb_dtype is None else (0 if wb_dtype == torch.float32 else 1), 0 if out_dtype == torch.float32 else 1,
+        _ptr(row_map), rows, width, _stream()), "gated_depth_dyt")
+    return z, [y for y in ys if y is not None]
+
+
+def xielu(x: torch.Tensor, coef: torch.Tensor) -> torch.Tensor:
+    """z > 0: a z^2 + z/2;  z <= 0: c (e^z - 1 - z) + z/2, with ``coef`` = (a, c) float32; same dtype out."""
+    _need(x, "x"); _need(coef, "coef", torch.float32)
+    if coef.numel() != 2:
+        raise KernelError("xielu needs two coefficients")
+    out = torch.empty_like(x)
+    _check(lib().hb_xielu(_ptr(x), _ptr(out), _dt(x), _ptr(coef), x.numel(), _stream()), "xielu")
+    return out
+
+
+# --------------------------------------------------------------------------- latent attention
+def _row_strided(t: torch.Tensor, name: str) -> int:
+    """A 2-D view whose rows are contiguous runs (a column slice of a contiguous matrix); its row stride."""
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor; this engine has no CPU path")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be a matrix with contiguous rows")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def latent_append(x: torch.Tensor, weight: torch.Tensor, eps: float, positions: torch.Tensor,
+                  seq_of_token: torch.Tensor, block_table: torch.Tensor, pages: torch.Tensor) -> None:
+    """pages[page of token, 0, place, :rank] = x / sqrt(mean(x^2) + eps) * weight for every token's row of
+    ``x`` [N, rank] (rows may be a column slice of a wider matrix); ``pages`` [P, 1, page_size, row_len >= rank],
+    the rest of a row is zero-filled. Statistics in float32."""
+    stride = _row_strided(x, "x")
+    _need(weight, "weight", x.dtype); _need(pages, "pages", x.dtype)
+    for t, nm in ((positions, "positions"), (seq_of_token, "seq_of_token"), (block_table, "block_table")):
+        _need(t, nm, torch.int32)
+    n, rank = x.shape
+    if pages.dim() != 4 or pages.shape[1] != 1 or pages.shape[3] < rank or weight.numel() != rank:
+        raise KernelError(f"pages {tuple(pages.shape)} / weight do not take latents of {rank}")
+    _check(lib().hb_latent_append(_ptr(x), _dt(x), stride, _ptr(weight), float(eps), _ptr(positions), _ptr(seq_of_token),
+                                  _ptr(block_table), block_table.shape[1], _ptr(pages), pages.shape[2], rank,
+                                  pages.shape[3], n, _stream()), "latent_append")
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x [N, heads, dim] * sigmoid(gate [N, heads]) per (token, head); ``gate`` may be a column slice."""
+    _need(x, "x")
+    stride = _row_strided(gate, "gate")
+    n, heads, dim = x.shape
+    if gate.dtype != x.dtype or tuple(gate.shape) != (n, heads):
+        raise KernelError("gate must be [N, heads] of x's dtype")
+    out = torch.empty_like(x)
+    _check(lib().hb_head_gate(_ptr(x), _ptr(gate), stride, _ptr(out), _dt(x), n, heads, dim, _stream()), "head_gate")
+    return out
+
+
+# --------------------------------------------------------------------------- gated delta rule
+def delta_prep(proj: torch.Tensor, chan_off: int, beta_off: int, taps: torch.Tensor, state: torch.Tensor,
+               conv_off: int, a_pre: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+               cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, heads: int, kvh: int,
+               dim: int, vdim: int):
+    """Per token: causal convolution over time (``taps`` float32 [C, K], last column = the token itself) and
+    silu of the C = 2*kvh*dim + heads*vdim channels q | k | v that start at column ``chan_off`` of ``proj``
+    [N, ld]; rows before a portion's first token come from ``state[slot, conv_off:]`` ([K-1, C] float32);
+    q and k to unit length per head (q also * dim^-1/2); beta = sigmoid(proj[:, beta_off + h]);
+    decay = exp(-exp(a_log[h]) * softplus(a_pre + dt_bias)). Returns float32 (q, k, v, beta, decay)."""
+    _need(proj, "proj"); _need(taps, "taps", torch.float32); _need(state, "state", torch.float32)
+    _need(a_pre, "a_pre"); _need(dt_bias, "dt_bias", torch.float32); _need(a_log, "a_log", torch.float32)
+    for t, nm in ((cu_seqlens, "cu_seqlens"), (seq_of_token, "seq_of_token"), (slots, "slots")):
+        _need(t, nm, torch.int32)
+    n, ld = proj.shape
+    c = 2 * kvh * dim + heads * vdim
+    k_taps = taps.shape[1]
+    if tuple(taps.shape) != (c, k_taps) or chan_off + c > ld or beta_off + heads > ld:
+        raise KernelError("taps / column offsets do not fit the projection")
+    if tuple(a_pre.shape) != (n, heads * dim) or dt_bias.numel() != heads * dim or a_log.numel() != heads:
+        raise KernelError("decay inputs do not match heads x dim")
+    if state.dim() != 2 or conv_off + (k_taps - 1) * c > state.shape[1]:
+        raise KernelError("the state does not hold the convolution's inputs")
+    dev, f32 = proj.device, torch.float32
+    q = torch.empty((n, kvh * dim), dtype=f32, device=dev)
+    k = torch.empty((n, kvh * dim), dtype=f32, device=dev)
+    v = torch.empty((n, heads * vdim), dtype=f32, device=dev)
+    beta = torch.empty((n, heads), dtype=f32, device=dev)
+    decay = torch.empty((n, heads * dim), dtype=f32, device=dev)
+    _check(lib().hb_delta_prep(_ptr(proj), _dt(proj), ld, int(chan_off), int(beta_off), _ptr(taps), _ptr(state),
+                               state.shape[1], int(conv_off), _ptr(a_pre), _dt(a_pre), _ptr(dt_bias), _ptr(a_log),
+                               _ptr(cu_seqlens), _ptr(seq_of_token), _ptr(slots), _ptr(q), _ptr(k), _ptr(v), _ptr(beta),
+                               _ptr(decay), n, heads, kvh, dim, vdim, k_taps, _stream()), "delta_prep")
+    return q, k, v, beta, decay
+
+
+def delta_conv_update(proj: torch.Tensor, chan_off: int, channels: int, taps_n: int, state: torch.Tensor,
+                      conv_off: int, cu_seqlens: torch.Tensor, slots: torch.Tensor) -> None:
+    """state[slot, conv_off:] <- the last K-1 convolution inputs of every request after this step's rows."""
+    _need(proj, "proj"); _need(state, "state", torch.float32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32); _need(slots, "slots", torch.int32)
+    if chan_off + channels > proj.shape[1] or conv_off + (taps_n - 1) * channels > state.shape[1]:
+        raise KernelError("channels do not fit the projection or the state")
+    _check(lib().hb_delta_conv_update(_ptr(proj), _dt(proj), proj.shape[1], int(chan_off), _ptr(state), state.shape[1],
+                                      int(conv_off), _ptr(cu_seqlens), _ptr(slots), slots.numel(), channels, taps_n,
+                                      _stream()), "delta_conv_update")
+
+
+def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor,
+                     state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, heads: int, kvh: int,
+                     dim: int, vdim: int, general: bool = False) -> torch.Tensor:
+    """Token after token per request and head, on ``state[slot, :heads*dim*vdim]`` ([heads, dim, vdim] float32):
+    S <- decay * S (per row); u = beta (v - S^T k); S <- S + k u^T; o = S^T q. Returns o float32 [N, heads*vdim].
+    ``general`` forces the kernel that keeps S in shared memory (any dim) instead of registers (dim <= 256)."""
+    for t, nm in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (decay, "decay"), (state, "state")):
+        _need(t, nm, torch.float32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32); _need(slots, "slots", torch.int32)
+    n = q.shape[0]
+    if tuple(q.shape) != (n, kvh * dim) or tuple(k.shape) != (n, kvh * dim) or tuple(v.shape) != (n, heads * vdim) or \
+            tuple(beta.shape) != (n, heads) or tuple(decay.shape) != (n, heads * dim):
+        raise KernelError("q / k / v / beta / decay do not match the head sizes")
+    if state.dim() != 2 or state.shape[1] < heads * dim * vdim or cu_seqlens.numel() != slots.numel() + 1:
+        raise KernelError("the state or the request tables do not fit")
+    out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
+    _check(lib().hb_delta_recurrence(_ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), state.shape[1],
+                                     _ptr(cu_seqlens), _ptr(slots), _ptr(out), slots.numel(), heads, kvh, dim, vdim,
+                                     int(general), _stream()), "delta_recurrence")
+    return out
+
+
+def delta_out_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, vdim: int,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """o [N, heads*vdim] float32 -> o / sqrt(mean over each head's vdim (o^2) + eps) * weight[vdim] *
+    sigmoid(gate), in ``out_dtype``."""
+    _need(o, "o", torch.float32); _need(gate, "gate"); _need(weight, "weight", out_dtype)
+    if o.shape != gate.shape or o.shape[1] % vdim or weight.numel() != vdim:
+        raise KernelError("gate / weight do not match the heads' value size")
+    out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    _check(lib().hb_delta_out_norm(_ptr(o), _ptr(gate), _dt(gate), _ptr(weight), float(eps), _ptr(out), _dt(out),
+                                   o.numel() // vdim, vdim, _stream()), "delta_out_norm")
     return out
 
 

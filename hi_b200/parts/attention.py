@@ -12,6 +12,59 @@ from .registry import build, register
 from .spec import CacheSpec, PartSpec, TensorSpec
 
 
+def _key_splits(ctx, nh: int, chunk: int, sliding: int, single: bool, device) -> int:
+    """Portions far into long contexts on a layer that sees every key: all blocks of the
+    tensor-core prefill kernel then have about the same many key tiles, and a partly filled
+    last round of blocks is worth splitting the keys for (ops.prefill_key_splits)."""
+    if chunk or sliding:
+        return 1
+    portions = [(s, n) for s, n in zip(ctx.start_pos, ctx.n_new) if n > 1 or not single]
+    if not portions:
+        return 1
+    shortest, longest_new = min(s for s, _n in portions), max(n for _s, n in portions)
+    if shortest < 2 * longest_new:
+        return 1
+    blocks = nh * sum(-(-n // ops.PREFILL_TC_MIN_TOKENS) for _s, n in portions)
+    return ops.prefill_key_splits(blocks, shortest // 64, ops.sm_count(device))
+
+
+def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, hd: int, chunk: int, sliding: int,
+                      scale: float):
+    """softmax(q k^T scale + mask) v for the step's tokens over the paged keys and values that are in
+    the cache already, by the kernel that fits the step: single decoded tokens, portions of prompts
+    (with single tokens of other requests beside them), or the general kernel for what those refuse
+    (float32, other head sizes). ``q`` [N, nh, hd] -> [N, nh, hd]. Every mixer whose scores are dot
+    products over paged rows comes through here; ``k_pages`` and ``v_pages`` may be the same pool."""
+    positions = ctx.positions
+    if ctx.max_new == 1 and ops.decode_attention_supported(q.dtype, nh, nkv, hd):
+        # every token of the step is one request's decoded token: the tensor-core kernel
+        return ops.decode_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions,
+                                    chunk, sliding, scale, ctx.max_context)
+    if ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, nh, nkv, hd):
+        # portions of prompts (single tokens of other requests ride along as one-row tiles)
+        single = ctx.decode_rows is not None and ops.decode_attention_supported(q.dtype, nh, nkv, hd)
+        # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync
+        tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(
+            q.dtype, nh, nkv, hd, ctx.page_size)
+        if tc:
+            o = ops.prefill_attention_tc(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions,
+                                         ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single,
+                                         key_splits=_key_splits(ctx, nh, chunk, sliding, single, q.device))
+        else:
+            o = ops.prefill_attention(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions,
+                                      ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single)
+        if single:
+            # single tokens beside portions: their long key ranges go through the split decode kernel
+            rows = ctx.decode_rows
+            od = ops.decode_attention(q.index_select(0, rows), k_pages, v_pages, block_table,
+                                      ctx.seq_of_token.index_select(0, rows), positions.index_select(0, rows),
+                                      chunk, sliding, scale, ctx.decode_max_context)
+            o.index_copy_(0, rows, od)
+        return o
+    return ops.paged_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions,
+                               chunk, sliding, scale, ctx.max_context)
+
+
 @register("mixer", "attention")
 class AttentionMixer(Part):
     """q/k/v projections, position encoding or temperature, optional weightless q/k norm, cache
@@ -85,21 +138,6 @@ class AttentionMixer(Part):
         b_o = fetch(f"{self.prefix}.o_proj.bias")
         self.b_o = None if b_o is None else b_o.to(self.w_o.dtype).contiguous()
 
-    def _key_splits(self, ctx, chunk: int, sliding: int, single: bool, device) -> int:
-        """Portions far into long contexts on a layer that sees every key: all blocks of the
-        tensor-core prefill kernel then have about the same many key tiles, and a partly filled
-        last round of blocks is worth splitting the keys for (ops.prefill_key_splits)."""
-        if chunk or sliding:
-            return 1
-        portions = [(s, n) for s, n in zip(ctx.start_pos, ctx.n_new) if n > 1 or not single]
-        if not portions:
-            return 1
-        shortest, longest_new = min(s for s, _n in portions), max(n for _s, n in portions)
-        if shortest < 2 * longest_new:
-            return 1
-        blocks = self.nh * sum(-(-n // ops.PREFILL_TC_MIN_TOKENS) for _s, n in portions)
-        return ops.prefill_key_splits(blocks, shortest // 64, ops.sm_count(device))
-
     def forward(self, normed, ctx, cache):
         qkv = linear(normed, self.w_qkv, bias=self.b_qkv)
         positions = ctx.positions
@@ -125,31 +163,6 @@ class AttentionMixer(Part):
         q = ops.qkv_post(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
                          self.qk_norm_eps, self.temperature, ctx.seq_of_token, block_table, cache.k_pages,
                          cache.v_pages, ctx.page_size, cache.writes)
-        if ctx.max_new == 1 and ops.decode_attention_supported(q.dtype, self.nh, self.nkv, self.hd):
-            # every token of the step is one request's decoded token: the tensor-core kernel
-            o = ops.decode_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
-                                     chunk, sliding, self.scale, ctx.max_context)
-        elif ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, self.nh, self.nkv, self.hd):
-            # portions of prompts (single tokens of other requests ride along as one-row tiles)
-            single = ctx.decode_rows is not None and ops.decode_attention_supported(q.dtype, self.nh, self.nkv, self.hd)
-            # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync
-            tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(
-                q.dtype, self.nh, self.nkv, self.hd, ctx.page_size)
-            if tc:
-                o = ops.prefill_attention_tc(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
-                                             ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single,
-                                             key_splits=self._key_splits(ctx, chunk, sliding, single, q.device))
-            else:
-                o = ops.prefill_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.cu_seqlens, positions,
-                                          ctx.n_seqs, ctx.max_new, chunk, sliding, self.scale, skip_single=single)
-            if single:
-                # single tokens beside portions: their long key ranges go through the split decode kernel
-                rows = ctx.decode_rows
-                od = ops.decode_attention(q.index_select(0, rows), cache.k_pages, cache.v_pages, block_table,
-                                          ctx.seq_of_token.index_select(0, rows), positions.index_select(0, rows),
-                                          chunk, sliding, self.scale, ctx.decode_max_context)
-                o.index_copy_(0, rows, od)
-        else:
-            o = ops.paged_attention(q, cache.k_pages, cache.v_pages, block_table, ctx.seq_of_token, positions,
-                                    chunk, sliding, self.scale, ctx.max_context)
+        o = attend_over_pages(q, cache.k_pages, cache.v_pages, block_table, ctx, self.nh, self.nkv, self.hd, chunk,
+                              sliding, self.scale)
         return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)

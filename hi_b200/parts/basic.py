@@ -8,7 +8,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .context import Pending
+from .context import GatedPending, Pending
 from .linear import linear
 from .registry import BuildEnv, build, register
 from .spec import PartSpec, TensorSpec
@@ -65,6 +65,70 @@ class RMSNorm(Part):
                 return ops.add_rmsnorm(residual, delta.dense, self.weight, self.eps, self.env.dtype, row_map, also_f32,
                                        delta.routed, delta.slot_of_entry, delta.top_k, delta.entry_weights)
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.env.dtype, row_map, also_f32)
+
+
+@register("norm", "dynamic_tanh")
+class DynamicTanh(Part):
+    """y = tanh(alpha x) * w + b: a norm that takes no mean or variance; alpha is one learned number.
+    params: ``size``, ``name``; tensors ``<prefix>`` (w), ``<prefix>.b``, ``<prefix>.alpha`` (a scalar).
+    alpha and the arithmetic are float32.
+
+    ``forward`` takes what the other norms take as ``delta`` (None, a tensor or a ``Pending``: added
+    into the stream in place) and also a :class:`~hi_b200.parts.context.GatedPending`, whose sum and
+    average give a NEW stream tensor; that form returns ``(stream, y)`` from :meth:`resolve`."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.size = int(params["size"])
+        self.weight = self.bias = self.alpha = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix, (self.size,), init="ones"),
+                TensorSpec(f"{self.prefix}.b", (self.size,), init="normal"),
+                TensorSpec(f"{self.prefix}.alpha", (), init="ones")]
+
+    def load(self, fetch):
+        self.weight = fetch(self.prefix).contiguous()
+        self.bias = fetch(f"{self.prefix}.b").to(self.weight.dtype).contiguous()
+        self.alpha = fetch(f"{self.prefix}.alpha").to(torch.float32).reshape(1).contiguous()
+
+    def triple(self):
+        return (self.alpha, self.weight, self.bias)
+
+    @staticmethod
+    def resolve(residual, pending, norms, out_dtype, row_map=None, want_stream=True):
+        """The stream after ``pending`` and the outputs of up to two norms of it, in one kernel:
+        ``(stream | None, [y])``. Without a ``GatedPending`` the stream is ``residual`` itself."""
+        triples = [n.triple() for n in norms]
+        if isinstance(pending, GatedPending):
+            z, ys = ops.gated_depth_dyt(residual, pending.terms, pending.history, pending.filled, pending.mix,
+                                        triples, out_dtype, row_map, want_z=want_stream)
+            return z, ys
+        if isinstance(pending, Pending):
+            pending = pending.materialize(residual.shape[0])
+        terms = [] if pending is None else [(pending, None)]
+        # a plain sum goes into the stream in place, as with the other norms
+        z, ys = ops.gated_depth_dyt(residual, terms, None, 0, None, triples, out_dtype, row_map,
+                                    want_z=bool(terms) and row_map is None)
+        if z is not None:
+            residual.copy_(z)
+        return residual, ys
+
+    @staticmethod
+    def open_history(residual, history, norms, out_dtype):
+        """The norms of the stream that enters the first layer, which the same kernel stores as
+        result 0 of ``history``."""
+        _z, ys = ops.gated_depth_dyt(residual, [], history, 0, None, [n.triple() for n in norms], out_dtype,
+                                     want_z=False)
+        return ys
+
+    def forward(self, residual: torch.Tensor, delta, row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
+        _stream, ys = self.resolve(residual, delta, [self], self.env.dtype, row_map, want_stream=False)
+        if also_f32:
+            return ys[0], ys[0].to(torch.float32)
+        return ys[0]
 
 
 # --------------------------------------------------------------------------- positions
@@ -199,3 +263,86 @@ class PreNormBlock(Part):
             h = layer.norm_feed_forward.forward(residual, pending)
             pending = layer.feed_forward.forward(h, ctx)
         return residual, pending
+
+
+@register("arrangement", "parallel_gated")
+class ParallelGatedBlock(Part):
+    """Mixer and feed-forward side by side on the same input, each result gated element by element,
+    and optionally a weighted average over depth:
+
+        h1 = norm1(x), h2 = norm2(x)
+        X_next = x + sigmoid(W1 h1 + c1) * mixer(h1) + sigmoid(W2 h2 + c2) * ff(h2)
+        x <- sum_j mix[j] X_j          (X_0 the embedding output, X_j the result of layer j - 1)
+
+    The sums, the average and both norms of the NEXT layer run in one kernel at the layer boundary
+    (``ops.gated_depth_dyt``): the block returns its results as a
+    :class:`~hi_b200.parts.context.GatedPending`, as the pre-norm block returns its ``Pending``.
+
+    params: ``hidden_size``; ``gated`` (default True); ``depth_average`` (default False): with it the
+    layer has ``<prefix>.dwa`` with one weight per result so far, this layer's included.
+    tensors: ``<prefix>.rg1`` [W, W], ``<prefix>.rg1.b`` [W] (and ``rg2`` when the layer has a
+    feed-forward); ``<prefix>.dwa``. The norms must be ``dynamic_tanh``."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.width = int(params["hidden_size"])
+        self.gated = bool(params.get("gated", True))
+        self.depth = bool(params.get("depth_average", False))
+        self.results_before = int(params.get("results_before", 0))     # entries of the history when the layer starts
+        self.total_results = int(params.get("total_results", 0))
+        self.has_ff = bool(params.get("feed_forward", True))
+        self.w_g = [None, None]
+        self.b_g = [None, None]
+        self.mix: Optional[torch.Tensor] = None
+
+    def _gates(self):
+        return ("rg1", "rg2") if self.has_ff else ("rg1",)
+
+    def tensor_specs(self):
+        specs = []
+        if self.gated:
+            for g in self._gates():
+                specs += [TensorSpec(f"{self.prefix}.{g}", (self.width, self.width)),
+                          TensorSpec(f"{self.prefix}.{g}.b", (self.width,))]
+        if self.depth:
+            specs.append(TensorSpec(f"{self.prefix}.dwa", (self.results_before + 1,)))
+        return specs
+
+    def load(self, fetch):
+        if self.gated:
+            for i, g in enumerate(self._gates()):
+                self.w_g[i] = fetch(f"{self.prefix}.{g}").contiguous()
+                self.b_g[i] = fetch(f"{self.prefix}.{g}.b").to(self.w_g[i].dtype).contiguous()
+        if self.depth:
+            self.mix = fetch(f"{self.prefix}.dwa").to(torch.float32).contiguous()
+
+    def forward(self, layer, residual, pending, ctx, cache_view):
+        norms = [layer.norm_mixer] + ([layer.norm_feed_forward] if self.has_ff else [])
+        if not all(isinstance(n, DynamicTanh) for n in norms):
+            raise TypeError(f"{self.prefix}: the parallel gated block works with dynamic_tanh norms")
+        history = ctx.scratch.get("depth_history") if self.depth else None
+        if self.depth and history is None:
+            # the stream that enters the first layer (the embedding output) is result 0
+            if self.results_before != 1:
+                raise RuntimeError(f"{self.prefix}: the depth average has no results of earlier layers to read")
+            history = torch.empty((self.total_results, *residual.shape), dtype=torch.float32, device=residual.device)
+            ctx.scratch["depth_history"] = history
+            if pending is not None:
+                residual, _ = DynamicTanh.resolve(residual, pending, [], self.env.dtype)
+            x, ys = residual, DynamicTanh.open_history(residual, history, norms, self.env.dtype)
+        else:
+            x, ys = DynamicTanh.resolve(residual, pending, norms, self.env.dtype)
+        if ctx.tap is not None:
+            ctx.tap(f"{self.prefix}.stream_in", x)        # debug: the stream as this layer reads it
+        h1 = ys[0]
+        terms = [(layer.mixer.forward(h1, ctx, cache_view),
+                  linear(h1, self.w_g[0], bias=self.b_g[0]) if self.gated else None)]
+        if self.has_ff:
+            h2 = ys[1]
+            f = layer.feed_forward.forward(h2, ctx)
+            if isinstance(f, Pending):
+                f = f.materialize(h2.shape[0])
+            terms.append((f, linear(h2, self.w_g[1], bias=self.b_g[1]) if self.gated else None))
+        return x, GatedPending(terms=terms, history=history, filled=self.results_before, mix=self.mix)

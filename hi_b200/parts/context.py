@@ -37,6 +37,9 @@ class StepContext:
     # context among them; None when the step is all portions or all single tokens
     decode_rows: Optional[torch.Tensor] = None
     decode_max_context: int = 0
+    # what parts of one forward pass hand to later parts of the same pass (emptied at its start):
+    # an arrangement that needs the results of earlier layers keeps them here
+    scratch: Dict[str, object] = field(default_factory=dict)
 
     @property
     def max_new(self) -> int:
@@ -52,6 +55,7 @@ class CacheView:
     v_pages: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None         # [max_slots, *state_shape]
     writes: bool = True                          # False: read another entry's cache, do not append
+    slot: Optional[int] = None                   # the cache slot's number (a key for per-pass scratch)
 
 
 @dataclass
@@ -74,3 +78,18 @@ class Pending:
         if self.routed is None:
             return self.dense
         return ops.moe_combine(self.routed, self.slot_of_entry, self.dense, n_tokens, self.top_k, self.entry_weights)
+
+
+@dataclass
+class GatedPending:
+    """What a block with gated, side-by-side sub-layers leaves for the next norm: the sub-layers'
+    results with what their gates' sigmoids take (``terms``: (delta, gate | None), [N, W] each), and,
+    where the model hands on a weighted average of all layer results so far, the history of those
+    results (float32 [entries, N, W], ``filled`` of them written) with this layer's weights
+    (float32 [filled + 1]). The norm that takes it adds the gated terms into the stream, stores the sum
+    as the next entry, averages, and normalises, in one kernel."""
+
+    terms: list
+    history: Optional[torch.Tensor] = None
+    filled: int = 0
+    mix: Optional[torch.Tensor] = None

@@ -58,6 +58,42 @@ class DenseSwiGLU(Part):
         return self.mlp.forward(normed)
 
 
+@register("feed_forward", "dense_mlp")
+class DenseMLP(Part):
+    """W_down act(W_up x): two products with an activation between them, no gate branch.
+
+    params: ``hidden_size``, ``intermediate_size``, ``activation``:
+      "xielu"  z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2, with the
+               two learned numbers (p, q) of ``<prefix>.act``; the coefficients are worked out once, in float32.
+    tensors: ``<prefix>.up`` [I, H], ``<prefix>.down`` [H, I], ``<prefix>.act`` [2]."""
+
+    graph_safe = True
+    ACTIVATIONS = ("xielu",)
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.activation = params.get("activation", "xielu")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"{prefix}: activation {self.activation!r} is not supported; known: {self.ACTIVATIONS}")
+        self.w_up = self.w_down = self.coef = None
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.up", (self.inter, self.hidden)),
+                TensorSpec(f"{self.prefix}.down", (self.hidden, self.inter)),
+                TensorSpec(f"{self.prefix}.act", (2,))]
+
+    def load(self, fetch):
+        self.w_up = fetch(f"{self.prefix}.up").contiguous()
+        self.w_down = fetch(f"{self.prefix}.down").contiguous()
+        pq = fetch(f"{self.prefix}.act").to(torch.float64)
+        soft = torch.nn.functional.softplus(pq)
+        self.coef = torch.stack([soft[0], 0.5 + soft[1]]).to(torch.float32).contiguous()
+
+    def forward(self, normed, ctx):
+        return linear(ops.xielu(linear(normed, self.w_up), self.coef), self.w_down)
+
+
 @register("feed_forward", "routed_experts")
 @register("feed_forward", "moe_sigmoid")
 class SigmoidRoutedExperts(Part):

@@ -7,7 +7,9 @@ import torch
 
 from . import attention as _attention  # noqa: F401  (registers the parts)
 from . import basic as _basic          # noqa: F401
+from . import delta_rule as _delta     # noqa: F401
 from . import feed_forward as _ffn     # noqa: F401
+from . import latent_attention as _latent  # noqa: F401
 from .context import CacheView, StepContext
 from .registry import BuildEnv, build
 from .spec import CacheSpec, ModelSpec, PartSpec, TensorSpec
@@ -25,12 +27,17 @@ class Layer:
 
         self.norm_mixer = build("norm", spec.norm_mixer, env, sub(spec.norm_mixer))
         self.mixer = build("mixer", spec.mixer, env, sub(spec.mixer))
-        self.norm_feed_forward = build("norm", spec.norm_feed_forward, env, sub(spec.norm_feed_forward))
-        self.feed_forward = build("feed_forward", spec.feed_forward, env, sub(spec.feed_forward))
-        self.arrangement = build("arrangement", PartSpec(spec.arrangement), env, spec.prefix)
+        self.norm_feed_forward = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.norm_feed_forward = build("norm", spec.norm_feed_forward, env, sub(spec.norm_feed_forward))
+            self.feed_forward = build("feed_forward", spec.feed_forward, env, sub(spec.feed_forward))
+        arrangement = spec.arrangement if isinstance(spec.arrangement, PartSpec) else PartSpec(spec.arrangement)
+        self.arrangement = build("arrangement", arrangement, env, spec.prefix)
 
     def parts(self):
-        return [self.norm_mixer, self.mixer, self.norm_feed_forward, self.feed_forward]
+        """The layer's parts that may hold tensors (the arrangement last: most have none)."""
+        parts = [self.norm_mixer, self.mixer, self.norm_feed_forward, self.feed_forward, self.arrangement]
+        return [p for p in parts if p is not None]
 
 
 class Model:
@@ -60,8 +67,7 @@ class Model:
             if slot not in writers:
                 raise ValueError(f"cache slot {slot} is read but no schedule entry writes it")
         self.loaded = False
-        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self.all_parts()) and \
-            all(getattr(l.arrangement, "graph_safe", False) for l in self.layers)
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self.all_parts())
 
     # ---- weights
     def all_parts(self):
@@ -87,6 +93,7 @@ class Model:
         (None when no logits are wanted: the final norm and the head are then skipped)."""
         if not self.loaded:
             raise RuntimeError("model weights are not loaded")
+        ctx.scratch = {}
         residual = self.embedding.forward(ctx.tokens)
         pending = None
         for entry in self.spec.schedule:
@@ -94,7 +101,7 @@ class Model:
             view = caches[entry.cache]
             if view.writes != entry.writes_cache:
                 view = CacheView(group=view.group, k_pages=view.k_pages, v_pages=view.v_pages, state=view.state,
-                                 writes=entry.writes_cache)
+                                 writes=entry.writes_cache, slot=view.slot)
             residual, pending = layer.arrangement.forward(layer, residual, pending, ctx, view)
         if logit_rows is None or logit_rows.numel() == 0:
             return None

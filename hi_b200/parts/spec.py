@@ -41,6 +41,8 @@ class CacheSpec:
     Per token: one key row and one value row of ``kv_heads * head_dim`` elements,
     kept for ``window``: ``None`` = all earlier tokens, ``("chunk", C)`` = tokens of
     the query's own block of C positions, ``("sliding", W)`` = the last W tokens.
+    ``values=False``: the mixer keeps one row per token only (a latent from which it makes
+    keys and values itself); no value pool is allocated and its view has ``v_pages`` None.
     Per request: ``state_shape`` elements of fixed size (``()`` = none).
     Mixers with equal paged needs share a page group (one block table per request).
     """
@@ -50,6 +52,7 @@ class CacheSpec:
     window: Optional[Tuple[str, int]] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
+    values: bool = True
 
     @property
     def paged(self) -> bool:
@@ -73,14 +76,16 @@ class CacheSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: its parts and how the block arranges them."""
+    """One layer: its parts and how the block arranges them. ``feed_forward`` and its norm may be
+    None (a layer that is a mixer only); ``arrangement`` is the registered name, or a PartSpec when
+    the arrangement has sizes, constants or tensors of its own."""
 
     prefix: str                      # tensor-name prefix, e.g. "model.layers.3"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norm_mixer: PartSpec
-    norm_feed_forward: PartSpec
-    arrangement: str = "prenorm"
+    norm_feed_forward: Optional[PartSpec]
+    arrangement: Any = "prenorm"
 
 
 @dataclass(frozen=True)
