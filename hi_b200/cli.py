@@ -83,10 +83,15 @@ def cmd_inspect(args) -> int:
         "architecture": arch.name, "architectures": list(getattr(cfg, "architectures", ())),
         "layers": [{"layer": i, "mixer": l.mixer.kind, "window": l.mixer.params.get("window"),
                     "position": (l.mixer.params.get("position") or {}).kind if l.mixer.params.get("position") else None,
-                    "feed_forward": l.feed_forward.kind} for i, l in enumerate(spec.layers)],
+                    "feed_forward": l.feed_forward.kind if l.feed_forward is not None else None,
+                    "arrangement": getattr(l.arrangement, "kind", l.arrangement)} for i, l in enumerate(spec.layers)],
         "schedule": [e.layer for e in spec.schedule],
         "parameters": params, "weight_bytes_bf16": 2 * params,
-        "kv_bytes_per_token_bf16": sum(2 * 2 * cs.kv_heads * cs.head_dim for cs in model.cache_specs.values() if cs),
+        "schedule_cache_slots": [e.cache for e in spec.schedule],
+        "kv_bytes_per_token_bf16": sum(2 * (2 if cs.values else 1) * cs.kv_heads * cs.head_dim
+                                       for cs in model.cache_specs.values() if cs),
+        "state_bytes_per_request": sum(4 * int(torch.Size(cs.state_shape).numel())
+                                       for cs in model.cache_specs.values() if cs and cs.state_shape),
         "config": {k: v for k, v in vars(cfg).items() if k != "raw"},
     }
     try:

@@ -13,9 +13,8 @@
 
 namespace {
 
-constexpr int kMaxDimsPerLane = 8;  // head_dim <= 256
-
-template <typename T>
+// DPL: output dimensions a lane holds; head_dim <= 32 * DPL (8: up to 256, 16: up to 512).
+template <typename T, int kMaxDimsPerLane>
 __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                                        const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                        int table_stride, const int* __restrict__ seq_of_token,
@@ -190,25 +189,26 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 ||
       chunk < 0 || window < 0)
     return HB_ERR_BAD_ARG;
-  if (hd <= 0 || hd % 8 != 0 || hd > 32 * kMaxDimsPerLane) return HB_ERR_UNSUPPORTED;
+  if (hd <= 0 || hd % 8 != 0 || hd > 512) return HB_ERR_UNSUPPORTED;
+  const bool wide = hd > 256;
   if (n_tokens == 0) return HB_OK;
   const int warps_per_block = 4;
   const long long warps = (long long)n_tokens * nh * max_splits;
   const long long blocks = (warps + warps_per_block - 1) / warps_per_block;
   if (blocks > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
   const size_t smem = (size_t)warps_per_block * hd * sizeof(float);
-  if (dtype == HB_DTYPE_F32)
-    paged_attention_kernel<float><<<(int)blocks, warps_per_block * 32, smem, stream>>>(
-        (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, seq_of_token,
-        positions, (float*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, split_size, max_splits,
-        part_acc, part_ml);
-  else if (dtype == HB_DTYPE_BF16)
-    paged_attention_kernel<__nv_bfloat16><<<(int)blocks, warps_per_block * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
-        table_stride, seq_of_token, positions, (__nv_bfloat16*)out, n_tokens, nh, nkv, hd, page_size, chunk,
-        window, scale, split_size, max_splits, part_acc, part_ml);
-  else
+#define HB_PAGED_ATTENTION(T, DPL)                                                                              \
+  paged_attention_kernel<T, DPL><<<(int)blocks, warps_per_block * 32, smem, stream>>>(                          \
+      (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, table_stride, seq_of_token, positions,    \
+      (T*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, split_size, max_splits, part_acc, part_ml)
+  if (dtype == HB_DTYPE_F32) {
+    if (wide) HB_PAGED_ATTENTION(float, 16); else HB_PAGED_ATTENTION(float, 8);
+  } else if (dtype == HB_DTYPE_BF16) {
+    if (wide) HB_PAGED_ATTENTION(__nv_bfloat16, 16); else HB_PAGED_ATTENTION(__nv_bfloat16, 8);
+  } else {
     return HB_ERR_BAD_ARG;
+  }
+#undef HB_PAGED_ATTENTION
   HB_LAUNCH_CHECK();
   if (max_splits > 1) {
     if (dtype == HB_DTYPE_F32)

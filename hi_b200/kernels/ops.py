@@ -499,8 +499,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         raise KernelError("cache pages do not match the query's head_dim")
     if nh % nkv:
         raise KernelError(f"{nh} query heads are not a multiple of {nkv} kv heads")
-    if hd % 16 != 0 or hd > 256:
-        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256)")
+    if hd % 16 != 0 or hd > 512:
+        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 512)")
     out = torch.empty_like(q)
     longest = max_context
     if chunk > 0:
