@@ -766,6 +766,168 @@ def case_sweep():
     ops.check_tc_status()
 
 
+# --------------------------------------------------------------------------- Vinurax beside the closest existing model
+def _vinurax_config(width, heads, ff, layers, vocab=32000, rank=128):
+    """Layers in the order latent, delta, latent reading the first one's cache, latent, ...; head sizes 128."""
+    def latent(src=None):
+        m = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": rank, "scale": 128 ** -0.5}
+        if src is not None:
+            m["kv_from"] = src
+        return {"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff}}
+    delta = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4,
+                                                "decay_rank": 64, "gate_rank": 64}, "mlp": {"kind": "dense", "ff": ff}}
+    order = []
+    for i in range(layers):
+        order.append(delta if i % 3 == 1 else latent(src=i - 2 if i % 3 == 2 else None))
+    return {"architecture": "Vinurax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": order}
+
+
+def _dense_llama_config(width, heads, ff, layers, vocab=32000):
+    """The closest existing model at equal size: attention with rotary positions over every key, dense SwiGLU
+    with the same number of feed-forward parameters (three matrices of 2/3 the inner size)."""
+    return {"architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text", "vocab_size": vocab, "hidden_size": width,
+            "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4),
+            "head_dim": 128, "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "rope_scaling": None,
+            "attention_chunk_size": 1 << 20, "nope_layer_interval": 0, "use_qk_norm": False,
+            "attn_temperature_tuning": False, "interleave_moe_layer_step": 0, "num_local_experts": 1,
+            "num_experts_per_tok": 1, "intermediate_size": 8, "intermediate_size_mlp": (2 * ff // 3 + 127) // 128 * 128,
+            "tie_word_embeddings": True, "max_position_embeddings": 1 << 20}
+
+
+def case_vinurax(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, context=4096):
+    """Prefill (one prompt of ``tokens`` in one step) and decode (``batch`` requests at ``context`` cached
+    tokens, captured steps) throughput of a Vinurax model with random weights beside a dense Llama-4-shaped
+    model of equal width, depth, heads and feed-forward parameters; then the new kernels alone beside their
+    like kernels, with bytes moved over the measured copy bandwidth. Markdown on standard output."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.kernels import ops
+
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn, reps=5, flush_l2=True):
+        fn()
+        ts = []
+        for _ in range(reps):
+            if flush_l2:
+                flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    print(f"peaks: {pk['hbm_gbs']:.0f} GB/s copy, {pk['bf16_tflops']:.0f} TFLOP/s bf16 ({pk['source']}); "
+          f"width {width}, {heads} heads of 128, feed-forward {ff}, {layers} layers, bf16, random weights\n")
+    print("| model | prefill tokens/s | ms | decode tokens/s | ms/step | weights GB | launches/decode step |\n|---|---|---|---|---|---|---|")
+    for name, cfg in (("Vinurax", _vinurax_config(width, heads, ff, layers)),
+                      ("dense Llama-4 shape", _dense_llama_config(width, heads, ff, layers))):
+        eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                                 kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1)
+        vocab = eng.vocab_size
+        weights = sum(2 * int(torch.Size(sp.shape).numel()) for sp in eng.model.tensor_specs() if sp.init != "absent") / 1e9
+        prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+
+        def prefill():
+            eng.step([StepEntry("p", prompt, [tokens - 1])])
+            eng.finish("p")
+        t_pre = timed(prefill, reps=3)
+        for i in range(batch):
+            eng.assume_cached(i, context)
+        toks = torch.randint(0, vocab, (64, batch), generator=g).tolist()
+        turn = [0]
+
+        def decode():
+            eng.step([StepEntry(i, [toks[turn[0] % 64][i]], [0]) for i in range(batch)], borrow=True)
+            turn[0] += 1
+        for _ in range(4):
+            decode()
+        before = ops.LAUNCHES[0]
+        t_dec = timed(decode, reps=9, flush_l2=False)
+        launches = (ops.LAUNCHES[0] - before) // 10
+        print(f"| {name} | {tokens / t_pre * 1e3:,.0f} | {t_pre:.2f} | {batch / t_dec * 1e3:,.0f} | {t_dec:.3f} | {weights:.2f} | {launches} |")
+        del eng
+        torch.cuda.empty_cache()
+
+    # ---- kernels alone: bytes that must move over the time, against the copy peak
+    bf = torch.bfloat16
+    dg = torch.Generator(device=DEV).manual_seed(0)
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=DEV, generator=dg).to(dt)
+    rows = []
+
+    def row(kind, name, ms, nbytes, note=""):
+        rows.append(f"| {kind} | {name} | {ms * 1e3:.1f} | {nbytes / 1e6:.1f} | {nbytes / ms / 1e6:,.0f} | "
+                    f"{nbytes / ms / 1e6 / pk['hbm_gbs']:.2f} | {note} |")
+
+    for n, what in ((tokens, "prefill"), (batch, "decode")):
+        x = rnd(n, width, dt=torch.float32)
+        d1, d2, g1, g2 = rnd(n, width), rnd(n, width), rnd(n, width), rnd(n, width)
+        depth = layers // 2
+        hist = rnd(layers + 1, n, width, dt=torch.float32)
+        mix = rnd(depth + 1, dt=torch.float32)
+        nrm = [(rnd(1, dt=torch.float32), rnd(width), rnd(width)) for _ in range(2)]
+        ms = timed(lambda: ops.gated_depth_dyt(x, [(d1, g1), (d2, g2)], hist, depth, mix, nrm, bf))
+        row(what, f"gated sum + average over {depth + 1} results + 2 Dynamic Tanh", ms,
+            n * width * (4 + 4 * 2 + 4 * depth + 4 + 4 + 2 * 2), "one launch per layer")
+        w = rnd(width)
+        ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-5, bf))
+        row(what, "like: residual add + RMSNorm", ms, n * width * (4 + 2 + 4 + 2), "two launches per layer")
+        up = rnd(n, ff)
+        coef = torch.tensor([0.7, 0.9], device=DEV)
+        ms = timed(lambda: ops.xielu(up, coef))
+        row(what, "xIELU", ms, n * ff * 4)
+        gu = rnd(n, 2 * (2 * ff // 3))
+        ms = timed(lambda: ops.swiglu(gu))
+        row(what, "like: SwiGLU", ms, n * (2 * ff // 3) * 6)
+    # the delta rule's kernels: a prompt of `tokens`, then `batch` single tokens
+    hd = heads * 128
+    C = 3 * hd
+    s_len = heads * 128 * 128
+    state = torch.zeros(batch + 1, s_len + 3 * C, device=DEV)
+    for n, seqs, what in ((tokens, 1, "prefill"), (batch, batch, "decode")):
+        proj = rnd(n, C + heads + 128)
+        taps = rnd(C, 4, dt=torch.float32)
+        a_pre = rnd(n, hd, dt=torch.float32)
+        dtb, alog = rnd(hd, dt=torch.float32), rnd(heads, dt=torch.float32)
+        cu = torch.arange(0, n + 1, n // seqs, dtype=torch.int32, device=DEV)
+        sot = torch.repeat_interleave(torch.arange(seqs, device=DEV), n // seqs).to(torch.int32)
+        slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
+        ms = timed(lambda: ops.delta_prep(proj, 0, C, taps, state, s_len, a_pre, dtb, alog, cu, sot, slots, heads, heads, 128, 128))
+        row(what, "delta rule: convolution, unit q/k, beta, decay", ms, n * (C * 2 + hd * 4 + (C + hd + heads) * 4))
+        q, k, v, beta, decay = ops.delta_prep(proj, 0, C, taps, state, s_len, a_pre, dtb, alog, cu, sot, slots, heads, heads, 128, 128)
+        ms = timed(lambda: ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128))
+        flops = n * heads * 128 * 128 * 2 * 3
+        row(what, "delta rule: recurrence", ms, n * (C + hd + heads + hd) * 4 + 2 * seqs * s_len * 4,
+            f"{flops / ms / 1e9:,.1f} TFLOP/s float32 of the recurrence's own arithmetic")
+        o, gate, wn = rnd(n, hd, dt=torch.float32), rnd(n, hd), rnd(128)
+        ms = timed(lambda: ops.delta_out_norm(o, gate, wn, 1e-5, 128, bf))
+        row(what, "delta rule: output norm and gate", ms, n * hd * (4 + 2 + 2))
+    print("\n| step | kernel | us | MB that must move | GB/s | of the copy peak | |\n|---|---|---|---|---|---|---|")
+    print("\n".join(rows))
+
+
+def case_delta_recurrence(tokens=2048, heads=16, seqs=1):
+    """The delta rule's recurrence alone, three launches (head sizes 128): for ncu."""
+    import torch
+
+    from hi_b200.kernels import ops
+
+    dg = torch.Generator(device=DEV).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, device=DEV, generator=dg)
+    hd, n = heads * 128, tokens * seqs
+    q, k, v = rnd(n, hd) / 128, torch.nn.functional.normalize(rnd(n, heads, 128), dim=-1).view(n, hd).contiguous(), rnd(n, hd)
+    beta, decay = torch.rand(n, heads, device=DEV), torch.rand(n, hd, device=DEV) * 0.2 + 0.8
+    state = torch.zeros(seqs, heads * 128 * 128, device=DEV)
+    cu = torch.arange(0, n + 1, tokens, dtype=torch.int32, device=DEV)
+    slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128)
+    torch.cuda.synchronize()
+
+
 def _timeline(run, warm, what):
     """Kernel starts and ends of one step from the profiler's activity records (real durations, with
     what runs beside what), as markdown: the first two layers' launches, then totals by kernel."""
@@ -837,7 +999,8 @@ def case_prefill_timeline(tokens=2048, layers=4):
 
 
 CASES = {"sweep": case_sweep, "decode_timeline": case_decode_timeline, "prefill_timeline": case_prefill_timeline, "decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
-         "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step}
+         "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step,
+         "vinurax": case_vinurax, "delta_recurrence": case_delta_recurrence}
 
 
 if __name__ == "__main__":

@@ -49,45 +49,57 @@ struct PrepArgs {
   int heads, kvh, dim, vdim, K;
 };
 
-__global__ void delta_prep_kernel(const PrepArgs a) {
-  extern __shared__ float y[];     // C values after convolution and silu
+// grid (tokens, groups of units), a warp per unit: a unit is one q head, one k head (dim channels each) or
+// one v head (vdim channels, with that head's beta and decays), so that a step of few tokens still fills
+// the GPU. A lane reads back only what it wrote itself, so the warp needs no barrier.
+__global__ void delta_prep_kernel(const PrepArgs a, int longest) {
+  extern __shared__ float y_all[];     // [warps][longest]: a unit's channels after convolution and silu
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  float* y = y_all + (size_t)warp * longest;
   const int t = blockIdx.x;
   const int s = a.seq_of_token[t];
   const int start = a.cu_seqlens[s];
   const int local = t - start;
   const int qk = a.kvh * a.dim, C = 2 * qk + a.heads * a.vdim, K = a.K;
   const float* conv = a.state + (size_t)a.slots[s] * a.state_stride + a.conv_off;   // [K-1, C]
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < K; ++j) {
-      const int rel = local - (K - 1) + j;
-      const float x = rel >= 0 ? ldf(a.proj, a.proj_dtype, (size_t)(start + rel) * a.ld + a.chan_off + c)
-                               : conv[(size_t)(K - 1 + rel) * C + c];
-      acc += a.taps[(size_t)c * K + j] * x;
-    }
-    y[c] = acc * sigmoid1(acc);
-  }
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const float qscale = 1.f / sqrtf((float)a.dim);
-  for (int g = warp; g < 2 * a.kvh; g += nwarps) {
-    const float* src = y + (size_t)g * a.dim;
+  const int units = 2 * a.kvh + a.heads;
+  for (int u = blockIdx.y * warps + warp; u < units; u += gridDim.y * warps) {
+    const bool is_v = u >= 2 * a.kvh;
+    const int len = is_v ? a.vdim : a.dim;
+    const int c0 = is_v ? 2 * qk + (u - 2 * a.kvh) * a.vdim : u * a.dim;
     float ss = 0.f;
-    for (int i = lane; i < a.dim; i += 32) ss += src[i] * src[i];
-    ss = hb::warp_sum(ss);
-    const float inv = 1.f / sqrtf(ss + 1e-6f);
-    const bool is_q = g < a.kvh;
-    float* dst = is_q ? a.q + (size_t)t * qk + (size_t)g * a.dim : a.k + (size_t)t * qk + (size_t)(g - a.kvh) * a.dim;
-    for (int i = lane; i < a.dim; i += 32) dst[i] = is_q ? src[i] * inv * qscale : src[i] * inv;
-  }
-  const int HV = a.heads * a.vdim, HD = a.heads * a.dim;
-  for (int i = threadIdx.x; i < HV; i += blockDim.x) a.v[(size_t)t * HV + i] = y[2 * qk + i];
-  for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
-    a.beta[(size_t)t * a.heads + h] = sigmoid1(ldf(a.proj, a.proj_dtype, (size_t)t * a.ld + a.beta_off + h));
-  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
-    const float x = ldf(a.a_pre, a.a_dtype, (size_t)t * HD + i) + a.dt_bias[i];
-    const float sp = x > 20.f ? x : log1pf(expf(x));
-    a.decay[(size_t)t * HD + i] = expf(-expf(a.a_log[i / a.dim]) * sp);
+    for (int i = lane; i < len; i += 32) {
+      const int c = c0 + i;
+      float acc = 0.f;
+      for (int j = 0; j < K; ++j) {
+        const int rel = local - (K - 1) + j;
+        const float x = rel >= 0 ? ldf(a.proj, a.proj_dtype, (size_t)(start + rel) * a.ld + a.chan_off + c)
+                                 : conv[(size_t)(K - 1 + rel) * C + c];
+        acc += a.taps[(size_t)c * K + j] * x;
+      }
+      const float v = acc * sigmoid1(acc);
+      y[i] = v;
+      ss += v * v;
+    }
+    if (is_v) {
+      const int h = u - 2 * a.kvh;
+      for (int i = lane; i < len; i += 32) a.v[(size_t)t * a.heads * a.vdim + (size_t)h * a.vdim + i] = y[i];
+      if (lane == 0)
+        a.beta[(size_t)t * a.heads + h] = sigmoid1(ldf(a.proj, a.proj_dtype, (size_t)t * a.ld + a.beta_off + h));
+      const float rate = expf(a.a_log[h]);
+      for (int i = lane; i < a.dim; i += 32) {
+        const size_t at = (size_t)t * a.heads * a.dim + (size_t)h * a.dim + i;
+        const float x = ldf(a.a_pre, a.a_dtype, at) + a.dt_bias[(size_t)h * a.dim + i];
+        const float sp = x > 20.f ? x : log1pf(expf(x));
+        a.decay[at] = expf(-rate * sp);
+      }
+    } else {
+      const float inv = 1.f / sqrtf(hb::warp_sum(ss) + 1e-6f);
+      const bool is_q = u < a.kvh;
+      float* dst = is_q ? a.q + (size_t)t * qk + (size_t)u * a.dim : a.k + (size_t)t * qk + (size_t)(u - a.kvh) * a.dim;
+      for (int i = lane; i < len; i += 32) dst[i] = is_q ? y[i] * inv * qscale : y[i] * inv;
+    }
   }
 }
 
@@ -133,65 +145,158 @@ __device__ __forceinline__ void stage_token(const RecurArgs& a, int t, int head,
   }
 }
 
-// A column of S in the registers of SPLIT lanes of one warp, 32 rows each: lane = part * (32 / SPLIT) + c
-// holds rows r * SPLIT + part (r < 32) of the warp's column c; rows beyond dim stay zero. dim <= 32 * SPLIT.
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* src) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* src) {      // both 16-byte aligned
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+constexpr int kRecurTokens = 8;     // tokens staged per chunk
+constexpr int kRecurThreads = 64;   // two warps a block
+
+// A column of S in the registers of SPLIT lanes of one warp, ROWS rows each: lane = part * (32 / SPLIT) + c
+// holds rows r * SPLIT + part (r < ROWS) of the warp's column c; rows beyond dim stay zero. dim <= ROWS * SPLIT.
 // The two dot products of a token are summed within a thread in four interleaved chains, then across
-// the SPLIT lanes by a butterfly: the order is fixed.
-template <int SPLIT>
-__global__ void __launch_bounds__(64) delta_recurrence_reg_kernel(const RecurArgs a) {
-  constexpr int DIMP = 32 * SPLIT, WCOLS = 32 / SPLIT;
-  __shared__ float stage[2][3 * DIMP];
+// the SPLIT lanes by a butterfly: the order is fixed by dim alone.
+// The tokens' k, q, decay, v and beta come into shared memory in chunks of kRecurTokens by cp.async, the next
+// chunk while this one is worked on, so the chain from token to token never waits for memory.
+// Layout of a token in a chunk: k[DIMP] q[DIMP] g[DIMP] v[block's columns] beta, padded to 16 bytes.
+template <int ROWS, int SPLIT>
+__global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(const RecurArgs a) {
+  constexpr int DIMP = ROWS * SPLIT, WCOLS = 32 / SPLIT, BCOLS = WCOLS * (kRecurThreads / 32), TB = kRecurTokens;
+  constexpr int TOK = 3 * DIMP + (BCOLS + 4) / 4 * 4;
+  extern __shared__ __align__(16) float sm[];     // [2][TB][TOK]
   const int head = blockIdx.y, seq = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane / WCOLS;
-  const int col = (blockIdx.x * (blockDim.x >> 5) + warp) * WCOLS + (lane % WCOLS);
+  const int bcol = warp * WCOLS + (lane % WCOLS);
+  const int col0 = blockIdx.x * BCOLS;
+  const int col = col0 + bcol;
   const bool active = col < a.vdim;
   const int kvhead = head / (a.heads / a.kvh);
   const int first = a.cu_seqlens[seq], last = a.cu_seqlens[seq + 1];
   if (first >= last) return;
-  float* S = a.state + (size_t)a.slots[seq] * a.state_stride + (size_t)head * a.dim * a.vdim;
-  float s[32];
+  const int dim = a.dim;
+  float* S = a.state + (size_t)a.slots[seq] * a.state_stride + (size_t)head * dim * a.vdim;
+  float s[ROWS];
 #pragma unroll
-  for (int r = 0; r < 32; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     const int i = r * SPLIT + part;
-    s[r] = (active && i < a.dim) ? S[(size_t)i * a.vdim + col] : 0.f;
+    s[r] = (active && i < dim) ? S[(size_t)i * a.vdim + col] : 0.f;
   }
-  stage_token(a, first, head, kvhead, stage[0], DIMP);
+  // what no copy ever writes: rows beyond dim (k = q = 0, decay 1) and columns beyond vdim (v = 0)
+  for (int e = threadIdx.x; e < 2 * TB * TOK; e += kRecurThreads) {
+    const int f = e % TOK;
+    sm[e] = (f >= 2 * DIMP && f < 3 * DIMP) ? 1.f : 0.f;
+  }
   __syncthreads();
-  for (int t = first; t < last; ++t) {
-    const float* cur = stage[(t - first) & 1] + part;
-    if (t + 1 < last) stage_token(a, t + 1, head, kvhead, stage[(t - first + 1) & 1], DIMP);
-    const float vj = active ? a.v[(size_t)t * a.heads * a.vdim + (size_t)head * a.vdim + col] : 0.f;
-    const float bt = a.beta[(size_t)t * a.heads + head];
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int r = 0; r < 32; ++r) {
-      s[r] *= cur[2 * DIMP + r * SPLIT];
-      acc[r & 3] = fmaf(s[r], cur[r * SPLIT], acc[r & 3]);
+  const int bcols = min(BCOLS, a.vdim - col0);
+  const bool wide = (dim & 3) == 0;                             // rows of k, q, decay in 16-byte pieces
+  const bool wide_v = (a.vdim & 3) == 0 && (bcols & 3) == 0;
+  auto stage = [&](int t0, int buf) {
+    const int cnt = min(TB, last - t0);
+    float* dst = sm + (size_t)buf * TB * TOK;
+    const size_t qk_row = (size_t)a.kvh * dim, g_row = (size_t)a.heads * dim, v_row = (size_t)a.heads * a.vdim;
+    if (wide) {
+      const int per = dim >> 2;
+      for (int e = threadIdx.x; e < cnt * per; e += kRecurThreads) {
+        const int tok = e / per, i = (e - tok * per) << 2;
+        float* d = dst + tok * TOK + i;
+        cp_async16(d, a.k + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
+        cp_async16(d + DIMP, a.q + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
+        cp_async16(d + 2 * DIMP, a.decay + (size_t)(t0 + tok) * g_row + (size_t)head * dim + i);
+      }
+    } else {
+      for (int e = threadIdx.x; e < cnt * dim; e += kRecurThreads) {
+        const int tok = e / dim, i = e - tok * dim;
+        float* d = dst + tok * TOK + i;
+        cp_async4(d, a.k + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
+        cp_async4(d + DIMP, a.q + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
+        cp_async4(d + 2 * DIMP, a.decay + (size_t)(t0 + tok) * g_row + (size_t)head * dim + i);
+      }
     }
-    float dot = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-#pragma unroll
-    for (int o = WCOLS; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float u = bt * (vj - dot);
-    float oa[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int r = 0; r < 32; ++r) {
-      s[r] = fmaf(cur[r * SPLIT], u, s[r]);
-      oa[r & 3] = fmaf(s[r], cur[DIMP + r * SPLIT], oa[r & 3]);
+    if (wide_v) {
+      const int per = bcols >> 2;
+      for (int e = threadIdx.x; e < cnt * per; e += kRecurThreads) {
+        const int tok = e / per, c = (e - tok * per) << 2;
+        cp_async16(dst + tok * TOK + 3 * DIMP + c, a.v + (size_t)(t0 + tok) * v_row + (size_t)head * a.vdim + col0 + c);
+      }
+    } else {
+      for (int e = threadIdx.x; e < cnt * bcols; e += kRecurThreads) {
+        const int tok = e / bcols, c = e - tok * bcols;
+        cp_async4(dst + tok * TOK + 3 * DIMP + c, a.v + (size_t)(t0 + tok) * v_row + (size_t)head * a.vdim + col0 + c);
+      }
     }
-    float out = (oa[0] + oa[1]) + (oa[2] + oa[3]);
-#pragma unroll
-    for (int o = WCOLS; o < 32; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-    if (active && part == 0) a.out[(size_t)t * a.heads * a.vdim + (size_t)head * a.vdim + col] = out;
+    for (int tok = threadIdx.x; tok < cnt; tok += kRecurThreads)
+      cp_async4(dst + tok * TOK + 3 * DIMP + BCOLS, a.beta + (size_t)(t0 + tok) * a.heads + head);
+  };
+  stage(first, 0);
+  cp_async_commit();
+  int buf = 0;
+  for (int t0 = first; t0 < last; t0 += TB, buf ^= 1) {
+    const bool more = t0 + TB < last;
+    if (more) stage(t0 + TB, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();          // everything but the group just committed: this chunk is in
     __syncthreads();
+    const int cnt = min(TB, last - t0);
+    for (int tok = 0; tok < cnt; ++tok) {
+      const float* base = sm + ((size_t)buf * TB + tok) * TOK;
+      const float* cur = base + part;
+      const float vj = base[3 * DIMP + bcol];
+      const float bt = base[3 * DIMP + BCOLS];
+      float kk[ROWS];
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        kk[r] = cur[r * SPLIT];
+        s[r] *= cur[2 * DIMP + r * SPLIT];
+        acc[r & 3] = fmaf(s[r], kk[r], acc[r & 3]);
+      }
+      float dot = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+      for (int o = WCOLS; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = bt * (vj - dot);
+      float oa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        s[r] = fmaf(kk[r], u, s[r]);
+        oa[r & 3] = fmaf(s[r], cur[DIMP + r * SPLIT], oa[r & 3]);
+      }
+      float out = (oa[0] + oa[1]) + (oa[2] + oa[3]);
+#pragma unroll
+      for (int o = WCOLS; o < 32; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+      if (active && part == 0) a.out[(size_t)(t0 + tok) * a.heads * a.vdim + (size_t)head * a.vdim + col] = out;
+    }
+    __syncthreads();             // the chunk is read: its buffer may take the chunk after the next
   }
   if (active) {
 #pragma unroll
-    for (int r = 0; r < 32; ++r) {
+    for (int r = 0; r < ROWS; ++r) {
       const int i = r * SPLIT + part;
-      if (i < a.dim) S[(size_t)i * a.vdim + col] = s[r];
+      if (i < dim) S[(size_t)i * a.vdim + col] = s[r];
     }
   }
+}
+
+template <int ROWS, int SPLIT>
+int launch_recurrence_reg(const RecurArgs& a, int n_seqs, cudaStream_t stream) {
+  constexpr int DIMP = ROWS * SPLIT, BCOLS = (32 / SPLIT) * (kRecurThreads / 32);
+  const size_t smem = (size_t)2 * kRecurTokens * (3 * DIMP + (BCOLS + 4) / 4 * 4) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(delta_recurrence_reg_kernel<ROWS, SPLIT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid((a.vdim + BCOLS - 1) / BCOLS, a.heads, n_seqs);
+  delta_recurrence_reg_kernel<ROWS, SPLIT><<<grid, kRecurThreads, smem, stream>>>(a);
+  return HB_OK;
 }
 
 // Any dim: the block's columns of S in shared memory, [dim][blockDim.x].
@@ -267,20 +372,20 @@ extern "C" int hb_delta_prep(const void* proj, int proj_dtype, long long ld, int
     return HB_ERR_BAD_ARG;
   if (heads <= 0 || kvh <= 0 || heads % kvh || dim <= 0 || vdim <= 0 || taps_n < 1 || n_tokens < 0) return HB_ERR_BAD_ARG;
   if (n_tokens == 0) return HB_OK;
-  const size_t C = 2 * (size_t)kvh * dim + (size_t)heads * vdim;
-  const size_t smem = C * sizeof(float);
-  if (smem > 200 * 1024) return HB_ERR_UNSUPPORTED;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  const int longest = dim > vdim ? dim : vdim;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * longest * sizeof(float);
+  if (smem > 48 * 1024) return HB_ERR_UNSUPPORTED;
   PrepArgs a;
   a.proj = proj; a.proj_dtype = proj_dtype; a.ld = ld; a.chan_off = chan_off; a.beta_off = beta_off; a.taps = taps;
   a.state = state; a.state_stride = state_stride; a.conv_off = conv_off; a.a_pre = a_pre; a.a_dtype = a_dtype;
   a.dt_bias = dt_bias; a.a_log = a_log; a.cu_seqlens = cu_seqlens; a.seq_of_token = seq_of_token; a.slots = slots;
   a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay;
   a.heads = heads; a.kvh = kvh; a.dim = dim; a.vdim = vdim; a.K = taps_n;
-  delta_prep_kernel<<<n_tokens, C >= 1024 ? 256 : 128, smem, stream>>>(a);
+  const int units = 2 * kvh + heads;
+  int per_token = (units + warps - 1) / warps;
+  if (per_token > 64) per_token = 64;
+  delta_prep_kernel<<<dim3(n_tokens, per_token), warps * 32, smem, stream>>>(a, longest);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -309,13 +414,14 @@ extern "C" int hb_delta_recurrence(const float* q, const float* k, const float* 
   a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay; a.state = state; a.state_stride = state_stride;
   a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.heads = heads; a.kvh = kvh; a.dim = dim; a.vdim = vdim;
   if (!force_general && dim <= 256) {
-    const int split = dim <= 32 ? 1 : (dim <= 64 ? 2 : (dim <= 128 ? 4 : 8));
-    const int cols = 2 * (32 / split);      // two warps a block
-    dim3 grid((vdim + cols - 1) / cols, heads, n_seqs);
-    if (split == 1) delta_recurrence_reg_kernel<1><<<grid, 64, 0, stream>>>(a);
-    else if (split == 2) delta_recurrence_reg_kernel<2><<<grid, 64, 0, stream>>>(a);
-    else if (split == 4) delta_recurrence_reg_kernel<4><<<grid, 64, 0, stream>>>(a);
-    else delta_recurrence_reg_kernel<8><<<grid, 64, 0, stream>>>(a);
+    // sixteen rows a lane up to dim 128 (more lanes per column: the chain from token to token is short and
+    // a single sequence still gives every SM a few warps), thirty-two beyond
+    const int code = dim <= 16 ? launch_recurrence_reg<16, 1>(a, n_seqs, stream)
+                   : dim <= 32 ? launch_recurrence_reg<16, 2>(a, n_seqs, stream)
+                   : dim <= 64 ? launch_recurrence_reg<16, 4>(a, n_seqs, stream)
+                   : dim <= 128 ? launch_recurrence_reg<16, 8>(a, n_seqs, stream)
+                                : launch_recurrence_reg<32, 8>(a, n_seqs, stream);
+    if (code != HB_OK) return code;
   } else {
     const int cols = vdim > 32 ? 64 : 32;
     dim3 grid((vdim + cols - 1) / cols, heads, n_seqs);

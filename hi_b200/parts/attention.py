@@ -36,13 +36,27 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
     (float32, other head sizes). ``q`` [N, nh, hd] -> [N, nh, hd]. Every mixer whose scores are dot
     products over paged rows comes through here; ``k_pages`` and ``v_pages`` may be the same pool."""
     positions = ctx.positions
-    if ctx.max_new == 1 and ops.decode_attention_supported(q.dtype, nh, nkv, hd):
+    # the decode kernel packs the query heads of one kv head into a 16-row tile; more heads on ONE shared kv
+    # head go through it sixteen at a time
+    per_call = nh if nkv > 1 or nh <= 16 else 16
+    decode_ok = ops.decode_attention_supported(q.dtype, per_call, nkv, hd)
+
+    def decode(rows_q, seq, pos, longest):
+        if per_call == nh:
+            return ops.decode_attention(rows_q, k_pages, v_pages, block_table, seq, pos, chunk, sliding, scale, longest)
+        out = torch.empty_like(rows_q)
+        for first in range(0, nh, per_call):
+            part = rows_q[:, first: first + per_call].contiguous()
+            out[:, first: first + per_call] = ops.decode_attention(part, k_pages, v_pages, block_table, seq, pos, chunk,
+                                                                   sliding, scale, longest)
+        return out
+
+    if ctx.max_new == 1 and decode_ok:
         # every token of the step is one request's decoded token: the tensor-core kernel
-        return ops.decode_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions,
-                                    chunk, sliding, scale, ctx.max_context)
+        return decode(q, ctx.seq_of_token, positions, ctx.max_context)
     if ctx.max_new > 1 and ops.prefill_attention_supported(q.dtype, nh, nkv, hd):
         # portions of prompts (single tokens of other requests ride along as one-row tiles)
-        single = ctx.decode_rows is not None and ops.decode_attention_supported(q.dtype, nh, nkv, hd)
+        single = ctx.decode_rows is not None and decode_ok
         # at least a tile of new tokens somewhere: the tcgen05 kernel; short portions: mma.sync
         tc = ctx.max_new >= ops.PREFILL_TC_MIN_TOKENS and ops.prefill_attention_tc_supported(
             q.dtype, nh, nkv, hd, ctx.page_size)
@@ -56,9 +70,8 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
         if single:
             # single tokens beside portions: their long key ranges go through the split decode kernel
             rows = ctx.decode_rows
-            od = ops.decode_attention(q.index_select(0, rows), k_pages, v_pages, block_table,
-                                      ctx.seq_of_token.index_select(0, rows), positions.index_select(0, rows),
-                                      chunk, sliding, scale, ctx.decode_max_context)
+            od = decode(q.index_select(0, rows), ctx.seq_of_token.index_select(0, rows), positions.index_select(0, rows),
+                        ctx.decode_max_context)
             o.index_copy_(0, rows, od)
         return o
     return ops.paged_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions,
