@@ -898,7 +898,8 @@ def case_vinurax(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, 
         ms = timed(lambda: ops.delta_prep(proj, 0, C, taps, state, s_len, a_pre, dtb, alog, cu, sot, slots, heads, heads, 128, 128))
         row(what, "delta rule: convolution, unit q/k, beta, decay", ms, n * (C * 2 + hd * 4 + (C + hd + heads) * 4))
         q, k, v, beta, decay = ops.delta_prep(proj, 0, C, taps, state, s_len, a_pre, dtb, alog, cu, sot, slots, heads, heads, 128, 128)
-        ms = timed(lambda: ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128))
+        ms = timed(lambda: ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128,
+                                                single_tokens=seqs == n))
         flops = n * heads * 128 * 128 * 2 * 3
         row(what, "delta rule: recurrence", ms, n * (C + hd + heads + hd) * 4 + 2 * seqs * s_len * 4,
             f"{flops / ms / 1e9:,.1f} TFLOP/s float32 of the recurrence's own arithmetic")
@@ -910,7 +911,7 @@ def case_vinurax(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, 
 
 
 def case_delta_recurrence(tokens=2048, heads=16, seqs=1):
-    """The delta rule's recurrence alone, three launches (head sizes 128): for ncu."""
+    """The delta rule's recurrence alone (head sizes 128), each of its register forms twice: for ncu, and timed."""
     import torch
 
     from hi_b200.kernels import ops
@@ -923,9 +924,14 @@ def case_delta_recurrence(tokens=2048, heads=16, seqs=1):
     state = torch.zeros(seqs, heads * 128 * 128, device=DEV)
     cu = torch.arange(0, n + 1, tokens, dtype=torch.int32, device=DEV)
     slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
-    for _ in range(3):
-        ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128)
-    torch.cuda.synchronize()
+    for rows in (16, 32):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128, rows=rows)
+        a.record()
+        ops.delta_recurrence(q, k, v, beta, decay, state, cu, slots, heads, heads, 128, 128, rows=rows)
+        b.record()
+        torch.cuda.synchronize()
+        print(f"{rows} rows a lane: {a.elapsed_time(b) * 1e3:.1f} us")
 
 
 def _timeline(run, warm, what):

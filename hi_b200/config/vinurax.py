@@ -87,7 +87,9 @@ class VinuraxConfig:
                 raise ConfigError(f"config.json: {where}.mixer sizes must be positive")
             if kind == "latent_attention":
                 src = get_key(m, "kv_from", int)
-                layer = VinuraxLayer(**common, kv_rank=need("kv_rank"), scale=need("scale", float), kv_from=src)
+                scale = get_key(m, "scale", float)          # the usual dim^-1/2 where the config names none
+                layer = VinuraxLayer(**common, kv_rank=need("kv_rank"), kv_from=src,
+                                     scale=common["dim"] ** -0.5 if scale is None else scale)
                 if layer.kv_rank <= 0:
                     raise ConfigError(f"config.json: {where}.mixer.kv_rank must be positive")
                 if src is not None:

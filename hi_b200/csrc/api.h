@@ -128,7 +128,8 @@ int hb_delta_conv_update(const void* proj, int proj_dtype, long long ld, int cha
                          int n_seqs, int channels, int taps_n, cudaStream_t stream);
 int hb_delta_recurrence(const float* q, const float* k, const float* v, const float* beta, const float* decay,
                         float* state, long long state_stride, const int* cu_seqlens, const int* slots, float* out,
-                        int n_seqs, int heads, int kvh, int dim, int vdim, int force_general, cudaStream_t stream);
+                        int n_seqs, int heads, int kvh, int dim, int vdim, int variant, int single_tokens,
+                        cudaStream_t stream);   // variant: 0 chosen by sizes, 1 S in shared memory, 16 / 32 rows a lane
 int hb_delta_out_norm(const float* o, const void* gate, int gate_dtype, const void* w, float eps, void* out, int dtype,
                       long long rows, int vdim, cudaStream_t stream);
 

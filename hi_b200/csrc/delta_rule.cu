@@ -406,21 +406,31 @@ extern "C" int hb_delta_conv_update(const void* proj, int proj_dtype, long long 
 extern "C" int hb_delta_recurrence(const float* q, const float* k, const float* v, const float* beta,
                                    const float* decay, float* state, long long state_stride, const int* cu_seqlens,
                                    const int* slots, float* out, int n_seqs, int heads, int kvh, int dim, int vdim,
-                                   int force_general, cudaStream_t stream) {
+                                   int variant, int single_tokens, cudaStream_t stream) {
   if (!q || !k || !v || !beta || !decay || !state || !cu_seqlens || !slots || !out) return HB_ERR_BAD_ARG;
   if (heads <= 0 || kvh <= 0 || heads % kvh || dim <= 0 || vdim <= 0 || n_seqs < 0) return HB_ERR_BAD_ARG;
   if (n_seqs == 0) return HB_OK;
   RecurArgs a;
   a.q = q; a.k = k; a.v = v; a.beta = beta; a.decay = decay; a.state = state; a.state_stride = state_stride;
   a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.heads = heads; a.kvh = kvh; a.dim = dim; a.vdim = vdim;
-  if (!force_general && dim <= 256) {
-    // sixteen rows a lane up to dim 128 (more lanes per column: the chain from token to token is short and
-    // a single sequence still gives every SM a few warps), thirty-two beyond
-    const int code = dim <= 16 ? launch_recurrence_reg<16, 1>(a, n_seqs, stream)
-                   : dim <= 32 ? launch_recurrence_reg<16, 2>(a, n_seqs, stream)
-                   : dim <= 64 ? launch_recurrence_reg<16, 4>(a, n_seqs, stream)
-                   : dim <= 128 ? launch_recurrence_reg<16, 8>(a, n_seqs, stream)
-                                : launch_recurrence_reg<32, 8>(a, n_seqs, stream);
+  if (variant != 1 && variant != 0 && variant != 16 && variant != 32) return HB_ERR_BAD_ARG;
+  if (variant != 1 && dim <= 256) {
+    // How many rows of a column a lane holds (`variant`, 0: chosen here). A step of single tokens is bound by
+    // moving the states: 32 rows a lane, the widest runs of a row per warp (8 requests x 16 heads of 128 x 128:
+    // 32 us against 37 us). A portion is bound by the chain from token to token: 16 rows a lane (2,048 tokens:
+    // 766 us against 953 us; 8 rows a lane gave 777 us and are not built).
+    const int rows = variant ? variant : (single_tokens && dim <= 128 ? 32 : 16);
+    int code = HB_ERR_UNSUPPORTED;
+    if (rows == 32)
+      code = dim <= 32 ? launch_recurrence_reg<32, 1>(a, n_seqs, stream)
+           : dim <= 64 ? launch_recurrence_reg<32, 2>(a, n_seqs, stream)
+           : dim <= 128 ? launch_recurrence_reg<32, 4>(a, n_seqs, stream)
+                        : launch_recurrence_reg<32, 8>(a, n_seqs, stream);
+    else
+      code = dim <= 32 ? launch_recurrence_reg<16, 2>(a, n_seqs, stream)
+           : dim <= 64 ? launch_recurrence_reg<16, 4>(a, n_seqs, stream)
+           : dim <= 128 ? launch_recurrence_reg<16, 8>(a, n_seqs, stream)
+                        : launch_recurrence_reg<16, 16>(a, n_seqs, stream);
     if (code != HB_OK) return code;
   } else {
     const int cols = vdim > 32 ? 64 : 32;

@@ -50,7 +50,7 @@ _SIGNATURES = {
     "hb_delta_prep": [P, I, c_longlong, I, I, P, P, c_longlong, c_longlong, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I,
                       I, I, I, P],
     "hb_delta_conv_update": [P, I, c_longlong, I, P, c_longlong, c_longlong, P, P, I, I, I, P],
-    "hb_delta_recurrence": [P, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, I, P],
+    "hb_delta_recurrence": [P, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, I, I, P],
     "hb_delta_out_norm": [P, P, I, P, F, P, I, c_longlong, I, P],
 }
 
@@ -370,10 +370,12 @@ def delta_conv_update(proj: torch.Tensor, chan_off: int, channels: int, taps_n: 
 
 def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor,
                      state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, heads: int, kvh: int,
-                     dim: int, vdim: int, general: bool = False) -> torch.Tensor:
+                     dim: int, vdim: int, general: bool = False, rows: int = 0, single_tokens: bool = False) -> torch.Tensor:
     """Token after token per request and head, on ``state[slot, :heads*dim*vdim]`` ([heads, dim, vdim] float32):
     S <- decay * S (per row); u = beta (v - S^T k); S <- S + k u^T; o = S^T q. Returns o float32 [N, heads*vdim].
-    ``general`` forces the kernel that keeps S in shared memory (any dim) instead of registers (dim <= 256)."""
+    ``general`` forces the kernel that keeps S in shared memory (any dim) instead of registers (dim <= 256);
+    ``rows`` (16, 32) forces how many rows of a column a lane holds, else ``single_tokens`` (every request
+    brings one token) decides: the order of the sums differs between the forms, by rounding only."""
     for t, nm in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (decay, "decay"), (state, "state")):
         _need(t, nm, torch.float32)
     _need(cu_seqlens, "cu_seqlens", torch.int32); _need(slots, "slots", torch.int32)
@@ -386,7 +388,7 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
     out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
     _check(lib().hb_delta_recurrence(_ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state), state.shape[1],
                                      _ptr(cu_seqlens), _ptr(slots), _ptr(out), slots.numel(), heads, kvh, dim, vdim,
-                                     int(general), _stream()), "delta_recurrence")
+                                     1 if general else int(rows), int(single_tokens), _stream()), "delta_recurrence")
     return out
 
 

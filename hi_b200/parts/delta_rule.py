@@ -101,6 +101,6 @@ class ChannelDeltaMixer(Part):
                                               self.heads, self.kvh, self.dim, self.vdim)
         ops.delta_conv_update(proj, 0, self.channels, self.taps, cache.state, self.s_len, ctx.cu_seqlens, ctx.slots)
         o = ops.delta_recurrence(q, k, v, beta, decay, cache.state, ctx.cu_seqlens, ctx.slots, self.heads, self.kvh,
-                                 self.dim, self.vdim, general=self.GENERAL_KERNEL)
+                                 self.dim, self.vdim, general=self.GENERAL_KERNEL, single_tokens=ctx.max_new == 1)
         y = ops.delta_out_norm(o, gate, self.w_norm, self.eps, self.vdim, proj.dtype)
         return linear(y, self.w_o)

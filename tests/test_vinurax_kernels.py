@@ -129,8 +129,8 @@ def _recurrence(q, k, v, beta, decay, S, heads, kvh, dim, vdim):
 
 @pytest.mark.parametrize("heads,kvh,dim,vdim", [(4, 4, 32, 32), (4, 2, 16, 24), (3, 1, 48, 70), (2, 2, 64, 16),
                                                (2, 1, 100, 40), (2, 2, 128, 128), (1, 1, 200, 33), (2, 1, 264, 20)])
-@pytest.mark.parametrize("general", [False, True])
-def test_delta_recurrence(heads, kvh, dim, vdim, general):
+@pytest.mark.parametrize("form", ["auto", "single", 16, 32, "general"])
+def test_delta_recurrence(heads, kvh, dim, vdim, form):
     ops = _ops()
     g = torch.Generator().manual_seed(heads * 1000 + dim)
     lens = [1, 37, 2, 5]
@@ -147,7 +147,8 @@ def test_delta_recurrence(heads, kvh, dim, vdim, general):
     dev = state.to(DEV)
     f = lambda t: t.float().to(DEV).contiguous()
     got = ops.delta_recurrence(f(q), f(k), f(v), f(beta), f(decay), dev, cu.to(DEV), torch.tensor(slots, dtype=torch.int32, device=DEV),
-                               heads, kvh, dim, vdim, general=general)
+                               heads, kvh, dim, vdim, general=form == "general", single_tokens=form == "single",
+                               rows=form if isinstance(form, int) else 0)
     after = dev.cpu()
     for s, (a, b) in enumerate(zip(cu[:-1].tolist(), cu[1:].tolist())):
         S0 = state[slots[s], : heads * dim * vdim].double().view(heads, dim, vdim)
