@@ -906,6 +906,21 @@ def case_vinurax(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, 
         o, gate, wn = rnd(n, hd, dt=torch.float32), rnd(n, hd), rnd(128)
         ms = timed(lambda: ops.delta_out_norm(o, gate, wn, 1e-5, 128, bf))
         row(what, "delta rule: output norm and gate", ms, n * hd * (4 + 2 + 2))
+    # what the mixers do to their projections before attention: the latent into its page, beside q/k/v encoding
+    for n, what in ((tokens, "prefill"), (batch, "decode")):
+        pages = n // PAGE + 1
+        pos = torch.arange(n, dtype=torch.int32, device=DEV)
+        sot = torch.zeros(n, dtype=torch.int32, device=DEV)
+        table = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages)
+        lat, wl = rnd(n, 128 + 64), rnd(128)
+        pool = torch.zeros(pages, 1, PAGE, 128, dtype=bf, device=DEV)
+        ms = timed(lambda: ops.latent_append(lat[:, 64:], wl, 1e-5, pos, sot, table, pool))
+        row(what, "latent: RMS norm into its page (latent 128)", ms, n * 128 * 4)
+        nkv = max(1, heads // 4)
+        qkv = rnd(n, (heads + 2 * nkv) * 128)
+        kp, vp = (torch.zeros(pages, nkv, PAGE, 128, dtype=bf, device=DEV) for _ in range(2))
+        ms = timed(lambda: ops.qkv_post(qkv, heads, nkv, 128, pos, None, False, False, 1e-6, None, sot, table, kp, vp, PAGE, True))
+        row(what, "like: q/k/v encoding and append (no rotation)", ms, n * (heads + 2 * nkv) * 128 * 4)
     print("\n| step | kernel | us | MB that must move | GB/s | of the copy peak | |\n|---|---|---|---|---|---|---|")
     print("\n".join(rows))
 

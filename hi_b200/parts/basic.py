@@ -265,6 +265,17 @@ class PreNormBlock(Part):
         return residual, pending
 
 
+_side_streams: Dict[torch.device, "torch.cuda.Stream"] = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    """One second stream per device for branches that run beside the main one."""
+    device = torch.device(device)
+    if device not in _side_streams:
+        _side_streams[device] = torch.cuda.Stream(device=device)
+    return _side_streams[device]
+
+
 @register("arrangement", "parallel_gated")
 class ParallelGatedBlock(Part):
     """Mixer and feed-forward side by side on the same input, each result gated element by element,
@@ -284,6 +295,8 @@ class ParallelGatedBlock(Part):
     feed-forward); ``<prefix>.dwa``. The norms must be ``dynamic_tanh``."""
 
     graph_safe = True
+    OVERLAP_BRANCHES = True      # steps of few tokens: the feed-forward branch on a second stream beside the mixer
+    OVERLAP_MAX_TOKENS = 128
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -318,6 +331,12 @@ class ParallelGatedBlock(Part):
         if self.depth:
             self.mix = fetch(f"{self.prefix}.dwa").to(torch.float32).contiguous()
 
+    def _feed_forward_term(self, layer, h2, ctx):
+        f = layer.feed_forward.forward(h2, ctx)
+        if isinstance(f, Pending):
+            f = f.materialize(h2.shape[0])
+        return (f, linear(h2, self.w_g[1], bias=self.b_g[1]) if self.gated else None)
+
     def forward(self, layer, residual, pending, ctx, cache_view):
         norms = [layer.norm_mixer] + ([layer.norm_feed_forward] if self.has_ff else [])
         if not all(isinstance(n, DynamicTanh) for n in norms):
@@ -337,12 +356,23 @@ class ParallelGatedBlock(Part):
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.stream_in", x)        # debug: the stream as this layer reads it
         h1 = ys[0]
+        second, side = None, None
+        if self.has_ff and self.OVERLAP_BRANCHES and h1.shape[0] <= self.OVERLAP_MAX_TOKENS:
+            # The two branches share nothing but their input. In a step of few tokens neither fills the GPU
+            # and the step is a chain of short kernels: the feed-forward branch runs on a second stream beside
+            # the mixer (in a captured step: a parallel branch of the graph) and joins before the boundary kernel.
+            cur, side = torch.cuda.current_stream(), _side_stream(h1.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                second = self._feed_forward_term(layer, ys[1], ctx)
+            ys[1].record_stream(side)
+            for t in second:
+                if t is not None:
+                    t.record_stream(cur)
         terms = [(layer.mixer.forward(h1, ctx, cache_view),
                   linear(h1, self.w_g[0], bias=self.b_g[0]) if self.gated else None)]
         if self.has_ff:
-            h2 = ys[1]
-            f = layer.feed_forward.forward(h2, ctx)
-            if isinstance(f, Pending):
-                f = f.materialize(h2.shape[0])
-            terms.append((f, linear(h2, self.w_g[1], bias=self.b_g[1]) if self.gated else None))
+            terms.append(second if second is not None else self._feed_forward_term(layer, ys[1], ctx))
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
         return x, GatedPending(terms=terms, history=history, filled=self.results_before, mix=self.mix)
