@@ -161,16 +161,18 @@ constexpr int kRecurTokens = 8;     // tokens staged per chunk
 constexpr int kRecurThreads = 64;   // two warps a block
 
 // A column of S in the registers of SPLIT lanes of one warp, ROWS rows each: lane = part * (32 / SPLIT) + c
-// holds rows r * SPLIT + part (r < ROWS) of the warp's column c; rows beyond dim stay zero. dim <= ROWS * SPLIT.
-// The two dot products of a token are summed within a thread in four interleaved chains, then across
-// the SPLIT lanes by a butterfly: the order is fixed by dim alone.
+// holds rows part * ROWS + r (r < ROWS) of the warp's column c; rows beyond dim stay zero. dim <= ROWS * SPLIT.
+// The dot products of a token are summed within a thread in two interleaved chains, then across
+// the SPLIT lanes by a butterfly: the order is fixed by the kernel's form alone.
 // The tokens' k, q, decay, v and beta come into shared memory in chunks of kRecurTokens by cp.async, the next
 // chunk while this one is worked on, so the chain from token to token never waits for memory.
 // Layout of a token in a chunk: k[DIMP] q[DIMP] g[DIMP] v[block's columns] beta, padded to 16 bytes.
 template <int ROWS, int SPLIT>
 __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(const RecurArgs a) {
-  constexpr int DIMP = ROWS * SPLIT, WCOLS = 32 / SPLIT, BCOLS = WCOLS * (kRecurThreads / 32), TB = kRecurTokens;
-  constexpr int TOK = 3 * DIMP + (BCOLS + 4) / 4 * 4;
+  // a lane's rows lie side by side in shared memory, 4 floats of padding after each lane's run, so that a lane
+  // reads them four at a time and the SPLIT runs of a warp fall into different banks
+  constexpr int RP = ROWS + 4, DIMP = RP * SPLIT, WCOLS = 32 / SPLIT, BCOLS = WCOLS * (kRecurThreads / 32);
+  constexpr int TB = kRecurTokens, TOK = 3 * DIMP + (BCOLS + 4) / 4 * 4;
   extern __shared__ __align__(16) float sm[];     // [2][TB][TOK]
   const int head = blockIdx.y, seq = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
   float s[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
-    const int i = r * SPLIT + part;
+    const int i = part * ROWS + r;
     s[r] = (active && i < dim) ? S[(size_t)i * a.vdim + col] : 0.f;
   }
   // what no copy ever writes: rows beyond dim (k = q = 0, decay 1) and columns beyond vdim (v = 0)
@@ -207,7 +209,7 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
       const int per = dim >> 2;
       for (int e = threadIdx.x; e < cnt * per; e += kRecurThreads) {
         const int tok = e / per, i = (e - tok * per) << 2;
-        float* d = dst + tok * TOK + i;
+        float* d = dst + tok * TOK + (i / ROWS) * RP + (i % ROWS);
         cp_async16(d, a.k + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
         cp_async16(d + DIMP, a.q + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
         cp_async16(d + 2 * DIMP, a.decay + (size_t)(t0 + tok) * g_row + (size_t)head * dim + i);
@@ -215,7 +217,7 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
     } else {
       for (int e = threadIdx.x; e < cnt * dim; e += kRecurThreads) {
         const int tok = e / dim, i = e - tok * dim;
-        float* d = dst + tok * TOK + i;
+        float* d = dst + tok * TOK + (i / ROWS) * RP + (i % ROWS);
         cp_async4(d, a.k + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
         cp_async4(d + DIMP, a.q + (size_t)(t0 + tok) * qk_row + (size_t)kvhead * dim + i);
         cp_async4(d + 2 * DIMP, a.decay + (size_t)(t0 + tok) * g_row + (size_t)head * dim + i);
@@ -248,30 +250,42 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
     const int cnt = min(TB, last - t0);
     for (int tok = 0; tok < cnt; ++tok) {
       const float* base = sm + ((size_t)buf * TB + tok) * TOK;
-      const float* cur = base + part;
+      const float* cur = base + part * RP;
       const float vj = base[3 * DIMP + bcol];
       const float bt = base[3 * DIMP + BCOLS];
+      // One pass gives all three dot products of the token over the decayed column s' = g * s:
+      //   s'.k (for u), s'.q and k.q, since the read-out of the updated column is (s' + k u).q = s'.q + u (k.q).
+      // One butterfly carries the three sums; the update s = s' + k u follows with nothing waiting on it
+      // but the next token.
       float kk[ROWS];
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      float ak[2] = {0.f, 0.f}, aq[2] = {0.f, 0.f}, akq[2] = {0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        kk[r] = cur[r * SPLIT];
-        s[r] *= cur[2 * DIMP + r * SPLIT];
-        acc[r & 3] = fmaf(s[r], kk[r], acc[r & 3]);
+      for (int r4 = 0; r4 < ROWS; r4 += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(cur + r4);
+        const float4 q4 = *reinterpret_cast<const float4*>(cur + DIMP + r4);
+        const float4 g4 = *reinterpret_cast<const float4*>(cur + 2 * DIMP + r4);
+        const float kv[4] = {k4.x, k4.y, k4.z, k4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w}, gv[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = r4 + e;
+          kk[r] = kv[e];
+          s[r] *= gv[e];
+          ak[r & 1] = fmaf(s[r], kv[e], ak[r & 1]);
+          aq[r & 1] = fmaf(s[r], qv[e], aq[r & 1]);
+          akq[r & 1] = fmaf(kv[e], qv[e], akq[r & 1]);
+        }
       }
-      float dot = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      float dot = ak[0] + ak[1], sq = aq[0] + aq[1], kq = akq[0] + akq[1];
 #pragma unroll
-      for (int o = WCOLS; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      for (int o = WCOLS; o < 32; o <<= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      }
       const float u = bt * (vj - dot);
-      float oa[4] = {0.f, 0.f, 0.f, 0.f};
+      const float out = fmaf(u, kq, sq);
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        s[r] = fmaf(kk[r], u, s[r]);
-        oa[r & 3] = fmaf(s[r], cur[DIMP + r * SPLIT], oa[r & 3]);
-      }
-      float out = (oa[0] + oa[1]) + (oa[2] + oa[3]);
-#pragma unroll
-      for (int o = WCOLS; o < 32; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+      for (int r = 0; r < ROWS; ++r) s[r] = fmaf(kk[r], u, s[r]);
       if (active && part == 0) a.out[(size_t)(t0 + tok) * a.heads * a.vdim + (size_t)head * a.vdim + col] = out;
     }
     __syncthreads();             // the chunk is read: its buffer may take the chunk after the next
@@ -279,7 +293,7 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
   if (active) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      const int i = r * SPLIT + part;
+      const int i = part * ROWS + r;
       if (i < dim) S[(size_t)i * a.vdim + col] = s[r];
     }
   }
@@ -287,7 +301,7 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
 
 template <int ROWS, int SPLIT>
 int launch_recurrence_reg(const RecurArgs& a, int n_seqs, cudaStream_t stream) {
-  constexpr int DIMP = ROWS * SPLIT, BCOLS = (32 / SPLIT) * (kRecurThreads / 32);
+  constexpr int DIMP = (ROWS + 4) * SPLIT, BCOLS = (32 / SPLIT) * (kRecurThreads / 32);
   const size_t smem = (size_t)2 * kRecurTokens * (3 * DIMP + (BCOLS + 4) / 4 * 4) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(delta_recurrence_reg_kernel<ROWS, SPLIT>,
