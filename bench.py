@@ -925,6 +925,27 @@ def case_vinurax(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, 
     print("\n".join(rows))
 
 
+def case_vinurax_step(tokens=2048, batch=8, context=4096, width=2048, heads=16, ff=8192, layers=3):
+    """One Vinurax prompt step and two decode steps with every kernel launched on its own (no captured graph),
+    three layers (latent, delta, latent reading the first one's cache): for a launch list under ncu."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+
+    eng = Engine.from_config(_vinurax_config(width, heads, ff, layers), seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                             kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1,
+                             use_cuda_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    for rep in range(2):
+        eng.step([StepEntry("p", torch.randint(0, eng.vocab_size, (tokens,), generator=g).tolist(), [tokens - 1])])
+        eng.finish("p")
+    for i in range(batch):
+        eng.assume_cached(i, context)
+    for _ in range(3):
+        eng.step([StepEntry(i, [int(torch.randint(0, eng.vocab_size, (1,), generator=g))], [0]) for i in range(batch)])
+    torch.cuda.synchronize()
+
+
 def case_delta_recurrence(tokens=2048, heads=16, seqs=1):
     """The delta rule's recurrence alone (head sizes 128), each of its register forms twice: for ncu, and timed."""
     import torch
@@ -1021,7 +1042,8 @@ def case_prefill_timeline(tokens=2048, layers=4):
 
 CASES = {"sweep": case_sweep, "decode_timeline": case_decode_timeline, "prefill_timeline": case_prefill_timeline, "decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
          "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step,
-         "vinurax": case_vinurax, "delta_recurrence": case_delta_recurrence}
+         "vinurax": case_vinurax, "delta_recurrence": case_delta_recurrence,
+         "vinurax_step": case_vinurax_step}
 
 
 if __name__ == "__main__":

@@ -248,6 +248,7 @@ __global__ void __launch_bounds__(kRecurThreads) delta_recurrence_reg_kernel(con
     cp_async_wait<1>();          // everything but the group just committed: this chunk is in
     __syncthreads();
     const int cnt = min(TB, last - t0);
+#pragma unroll 2      // the next token's loads do not wait for this token's update
     for (int tok = 0; tok < cnt; ++tok) {
       const float* base = sm + ((size_t)buf * TB + tok) * TOK;
       const float* cur = base + part * RP;

@@ -69,6 +69,7 @@ def test_gated_depth_dyt(width, dt):
 def test_xielu(dt):
     ops = _ops()
     z = torch.cat([torch.linspace(-12, 12, 4001), torch.tensor([0.0, -0.0, 1e-4, -1e-4, 30.0, -60.0])]).to(dt)
+    z = z if dt == torch.float32 else torch.cat([z, z[:1]])     # 4,008 elements: the eight-at-a-time bfloat16 kernel
     pq = torch.tensor([0.3, -1.1], dtype=torch.float64)
     want = plain.xielu(z.double(), pq)
     coef = torch.stack([F.softplus(pq[0]), 0.5 + F.softplus(pq[1])]).float()
@@ -76,6 +77,8 @@ def test_xielu(dt):
     err = (got.double().cpu() - want).abs() / (want.abs() + z.double().abs() + 1e-3)    # y has a root near z = -2.5
     worst = int(err.argmax())
     assert float(err.max()) <= (2e-6 if dt == torch.float32 else 5e-3), (float(z[worst]), float(got[worst]), float(want[worst]))
+    ragged = ops.xielu(z[:-3].contiguous().to(DEV), coef.to(DEV))          # a count that is no multiple of eight
+    assert torch.equal(ragged.cpu(), got[:-3].cpu())
 
 
 @pytest.mark.parametrize("rank,row_len", [(128, 128), (40, 48), (72, 80)])
