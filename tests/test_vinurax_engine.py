@@ -10,12 +10,12 @@ import torch
 
 import harness as h
 import plain_vinurax as plain
-from vinurax_configs import VX_A, VX_B, VX_C, VX_D, make_weights, peaked, write_model
+from vinurax_configs import VX_A, VX_B, VX_C, VX_D, VX_E, make_weights, peaked, write_model
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 TOL = {"float32": 3e-5, "bfloat16": 4e-2}
-CONFIGS = {"A": VX_A, "B": VX_B, "C": VX_C, "D": VX_D}
+CONFIGS = {"A": VX_A, "B": VX_B, "C": VX_C, "D": VX_D, "E": VX_E}
 
 
 @pytest.fixture(scope="module")
@@ -168,7 +168,7 @@ def test_channel_delta_mixer_alone(dt, tol, heads, kvh, dim, vdim, taps, general
 
 
 # --------------------------------------------------------------------------- the model in the engine
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_four_ways_of_cutting(name, dtype, models):
     cfg, mdir, weights = models[name]

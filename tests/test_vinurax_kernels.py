@@ -131,7 +131,8 @@ def _recurrence(q, k, v, beta, decay, S, heads, kvh, dim, vdim):
 
 
 @pytest.mark.parametrize("heads,kvh,dim,vdim", [(4, 4, 32, 32), (4, 2, 16, 24), (3, 1, 48, 70), (2, 2, 64, 16),
-                                               (2, 1, 100, 40), (2, 2, 128, 128), (1, 1, 200, 33), (2, 1, 264, 20)])
+                                               (2, 1, 100, 40), (2, 2, 128, 128), (1, 1, 200, 33), (2, 1, 264, 20),
+                                               (2, 1, 18, 10), (3, 3, 5, 7)])
 @pytest.mark.parametrize("form", ["auto", "single", 16, 32, "general"])
 def test_delta_recurrence(heads, kvh, dim, vdim, form):
     ops = _ops()

@@ -8,10 +8,10 @@ import pytest
 import torch
 
 import plain_vinurax as plain
-from vinurax_configs import VX_A, VX_B, VX_C, VX_D, config, delta, latent, make_weights, write_model
+from vinurax_configs import VX_A, VX_B, VX_C, VX_D, VX_E, config, delta, latent, make_weights, write_model
 
 
-@pytest.mark.parametrize("cfg", [VX_A, VX_B, VX_C, VX_D])
+@pytest.mark.parametrize("cfg", [VX_A, VX_B, VX_C, VX_D, VX_E])
 def test_plain_model_portions_equal_whole(cfg):
     w = make_weights(cfg, 5)
     m = plain.PlainVinurax(cfg, w)
@@ -99,7 +99,7 @@ def test_inner_sizes_come_from_the_checkpoint_and_names_bind(tmp_path):
     from hi_b200.weights.loader import check_names
     from hi_b200.weights.safetensors_io import Checkpoint
 
-    for k, cfg in enumerate((VX_A, VX_B, VX_C, VX_D)):
+    for k, cfg in enumerate((VX_A, VX_B, VX_C, VX_D, VX_E)):
         d = str(tmp_path / f"m{k}")
         weights = write_model(d, cfg, 3, decay_rank=7, gate_rank=3)
         arch, typed, _raw = load_architecture(d)

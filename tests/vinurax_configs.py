@@ -49,6 +49,12 @@ VX_C = config(64, 48, 1e-5, [delta(2, 2, 16, 16, 3, ff=64), delta(3, 3, 8, 20, 5
 VX_D = config(90, 40, 1e-5, [latent(2, 8, 8, 32, 0.4, ff=40), latent(5, 8, 4, 32, 0.3, kv_from=0), latent(2, 4, 12, 24, 0.5)])
 
 
+# sizes that no kernel's wide path takes: width, head sizes, latent size, feed-forward and vocabulary
+# that are no multiples of four
+VX_E = config(77, 50, 1e-5, [latent(3, 10, 6, 22, 0.3, ff=30), delta(2, 1, 18, 10, 3, ff=26), latent(1, 6, 14, 22, 0.4, kv_from=0),
+                             delta(3, 3, 5, 7, 2)])
+
+
 def peaked(cfg: dict, factor: float) -> dict:
     """The same model with every attention scale multiplied: the softmax then puts nearly all of its
     weight on one key, often a far one, so a key that is lost, doubled or shifted shows in the logits."""
