@@ -284,3 +284,22 @@ def test_trace_replay_as_a_user_runs_it(models, tmp_path):
         got = h.replay_subprocess(mdir, dtype, steps, max_tokens=192, out_dir=str(tmp_path / dtype), vocab=cfg["vocab"],
                                   extra=["--max-live", "4"])
         compare(cfg, weights, requests, got, TOL[dtype], f"trace_run {dtype}")
+
+
+def test_command_line_run(models, capsys):
+    """``python -m hi_b200 run``: the next token, the top logits and greedy generation of a Vinurax folder."""
+    import json
+
+    from hi_b200.cli import main
+
+    cfg, mdir, weights = models["D"]
+    prompt = tokens(cfg, 12, 50)
+    assert main(["run", mdir, "--tokens", ",".join(map(str, prompt)), "--max-tokens", "5", "--top-k", "3",
+                 "--dtype", "float32", "--kv-page-size", "16", "--include-logits"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    model = plain.PlainVinurax(cfg, weights)
+    ref = model.logits(prompt)[-1]
+    assert report["next_token"] == int(ref.argmax()) and report["logit_count"] == cfg["vocab"]
+    assert float((torch.tensor(report["logits"], dtype=torch.float64) - ref).abs().max()) <= 3e-5 * float(ref.abs().max())
+    assert [t["token_id"] for t in report["top_logits"]] == torch.topk(ref, 3).indices.tolist()
+    assert len(report["generated_tokens"]) == 5 and report["generated_tokens"][0] == report["next_token"]
