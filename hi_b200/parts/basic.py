@@ -356,21 +356,25 @@ class ParallelGatedBlock(Part):
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.stream_in", x)        # debug: the stream as this layer reads it
         h1 = ys[0]
-        second, side = None, None
+        second, gate1, side = None, None, None
         if self.has_ff and self.OVERLAP_BRANCHES and h1.shape[0] <= self.OVERLAP_MAX_TOKENS:
             # The two branches share nothing but their input. In a step of few tokens neither fills the GPU
-            # and the step is a chain of short kernels: the feed-forward branch runs on a second stream beside
-            # the mixer (in a captured step: a parallel branch of the graph) and joins before the boundary kernel.
+            # and the step is a chain of short kernels: the feed-forward branch and the mixer's gate run on a
+            # second stream beside the mixer (in a captured step: a parallel branch of the graph) and join
+            # before the boundary kernel.
             cur, side = torch.cuda.current_stream(), _side_stream(h1.device)
             side.wait_stream(cur)
             with torch.cuda.stream(side):
                 second = self._feed_forward_term(layer, ys[1], ctx)
-            ys[1].record_stream(side)
-            for t in second:
+                gate1 = linear(h1, self.w_g[0], bias=self.b_g[0]) if self.gated else None
+            for t in ys:
+                t.record_stream(side)
+            for t in (*second, gate1):
                 if t is not None:
                     t.record_stream(cur)
-        terms = [(layer.mixer.forward(h1, ctx, cache_view),
-                  linear(h1, self.w_g[0], bias=self.b_g[0]) if self.gated else None)]
+        elif self.gated:
+            gate1 = linear(h1, self.w_g[0], bias=self.b_g[0])
+        terms = [(layer.mixer.forward(h1, ctx, cache_view), gate1)]
         if self.has_ff:
             terms.append(second if second is not None else self._feed_forward_term(layer, ys[1], ctx))
         if side is not None:
