@@ -4,9 +4,11 @@ architecture is added the same way from anywhere: a typed config reader, a build
 :func:`~hi_b200.config.registry.register_architecture` under its ``architectures`` /
 ``model_type`` names (the reference routes ``llama4`` / ``llama4_text`` to its Llama 4 model:
 crates/hi-mlx/src/config.rs:620-637, crates/hi-mlx/src/models.rs:373-375)."""
+from .config import fidatar as _fidatar
 from .config import vinurax as _vinurax
 from .config.llama4 import Llama4TextConfig
 from .config.registry import Architecture, register_architecture
+from .parts.fidatar import build_fidatar_spec, normalize_fidatar_tensor_name
 from .parts.llama4 import build_llama4_spec, derive_llama4_tensors, normalize_llama4_tensor_name
 from .parts.vinurax import build_vinurax_spec, normalize_vinurax_tensor_name
 
@@ -19,3 +21,8 @@ register_architecture(
     ["Vinurax", "vinurax"],
     Architecture(name="vinurax", parse_config=_vinurax.VinuraxConfig.from_json, build_spec=build_vinurax_spec,
                  normalize_tensor_name=normalize_vinurax_tensor_name, sizes_from_tensors=_vinurax.sizes_from_tensors))
+
+register_architecture(
+    ["Fidatar", "fidatar"],
+    Architecture(name="fidatar", parse_config=_fidatar.FidatarConfig.from_json, build_spec=build_fidatar_spec,
+                 normalize_tensor_name=normalize_fidatar_tensor_name))

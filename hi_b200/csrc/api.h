@@ -10,40 +10,49 @@ extern "C" {
 
 int hb_feed_tokens(int* tokens, const int* dst, const int* src, const int* sampled, int n, cudaStream_t stream);
 int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int n, int hidden,
-                    int vocab, cudaStream_t stream);
+                    int vocab, float scale, cudaStream_t stream);
 // routed_weight (or null): [n * top_k] factors of the routed rows in the sum (a score that scales the
-// experts' outputs)
+// experts' outputs). The sum takes x_scale * x; post != 0: the stream takes the normalised row, not the sum.
 int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed, const int* slot_of_entry,
                    const float* routed_weight, int top_k, const void* w, int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
-                   int rows, int hidden, float eps, cudaStream_t stream);
+                   int rows, int hidden, float eps, float x_scale, int post, cudaStream_t stream);
 int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream);
+int hb_relu2(const void* in, int dtype, void* out, int out_dtype, long long n, cudaStream_t stream);   // max(x, 0)^2
+int hb_softcap(float* x, float cap, long long n, cudaStream_t stream);                     // cap tanh(x / cap), in place
 int hb_moe_combine(const float* y, const int* slot_of_entry, const float* routed_weight, const void* shared,
                    int shared_dtype, float* out,
                    int n, int hidden, int top_k, cudaStream_t stream);
 
+// q_norm_w / k_norm_w (float32 [hd] or null), norm_first, norm_dim (<= hd; 0: hd), rot_mul: an RMS norm of q and
+// k with a weight per dim, over the first norm_dim dims of a head, before the rotation (else: the weightless
+// norm after it), and a factor on cos and sin; what the lane-per-16-dims kernel cannot take runs in a general one
 int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs, int interleaved, int qk_norm,
-                float qk_eps, int temp_on, float floor_scale, float attn_scale, const int* positions,
+                float qk_eps, int temp_on, float floor_scale, float attn_scale, const float* q_norm_w,
+                const float* k_norm_w, int norm_first, int norm_dim, float rot_mul, const int* positions,
                 const int* seq_of_token, const int* block_table, int table_stride, void* q_out, void* k_pages,
                 void* v_pages, int page_size, int write_kv, int n_tokens, int nh, int nkv, int hd,
                 cudaStream_t stream);
 
+// sink != 0 (every attention entry point): the softmax's denominator has one more term of score 0,
+// p_j = e^{s_j} / (1 + sum e^{s_j}); the term has no value
 int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                        const int* block_table, int table_stride, const int* seq_of_token, const int* positions,
                        void* out, int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
-                       float scale, int split_size, int max_splits, float* part_acc, float* part_ml,
+                       float scale, int sink, int split_size, int max_splits, float* part_acc, float* part_ml,
                        cudaStream_t stream);
 
 int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_rows, int hd,
-                       int max_splits, cudaStream_t stream);
+                       int max_splits, int sink, cudaStream_t stream);
 int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
-                        int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
-                        int max_splits, float* part_acc, float* part_ml, cudaStream_t stream);
+                        int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int sink,
+                        int split_size, int max_splits, float* part_acc, float* part_ml, cudaStream_t stream);
 
 int hb_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, int n_pages, const int* block_table,
                             int table_stride, const int* seq_of_token, const int* positions, void* out, int n_tokens,
-                            int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int split_size,
-                            int max_splits, float* part_acc, float* part_ml, int* status, cudaStream_t stream);
+                            int nh, int nkv, int hd, int page_size, int chunk, int window, float scale, int sink,
+                            int split_size, int max_splits, float* part_acc, float* part_ml, int* status,
+                            cudaStream_t stream);
 
 // hb_qkv_post, hb_attention_decode_tma and hb_attention_merge in one launch (attention_decode_tma.cu)
 int hb_attention_decode_fused(const void* qkv, const float* inv_freq, int rot_pairs, int interleaved, int qk_norm,
@@ -57,26 +66,28 @@ int hb_attention_decode_fused(const void* qkv, const float* inv_freq, int rot_pa
 int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                          int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_seqs,
                          int max_new, int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,
-                         int skip_single, cudaStream_t stream);
+                         int skip_single, int sink, cudaStream_t stream);
 
 int hb_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                             int table_stride, const int* cu_seqlens, const int* positions, void* out, int n_tokens,
                             int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
-                            int window, float scale, int skip_single, int key_splits, float* part_acc, float* part_ml,
-                            int* status, cudaStream_t stream);
+                            int window, float scale, int skip_single, int sink, int key_splits, float* part_acc,
+                            float* part_ml, int* status, cudaStream_t stream);
 
 // mode: bit 0 = scores are the softmax over all experts (clear: the sigmoid of the chosen logit),
-// bit 1 = the chosen scores are divided by their sum
+// bit 1 = the chosen scores are divided by their sum; bits 8-15 = G, 16-23 = KEEP: only experts of the KEEP best
+// of G equal groups of neighbours can be chosen (a group counts as the sum of its two largest sigmoid scores)
 int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
-                   int top_k, int mode, float* logits_out, int* ids, float* scores, cudaStream_t stream);
+                   int top_k, int mode, float score_scale, float* logits_out, int* ids, float* scores,
+                   cudaStream_t stream);    // score_scale: a constant factor on every chosen score
 int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
                 int* slot_of_entry, int* active, cudaStream_t stream);
 int hb_router_plan(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts, int top_k,
-                   int mode, float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
-                   int* active, int* counter, cudaStream_t stream);
+                   int mode, float score_scale, float* logits_out, int* ids, float* scores, int* offsets,
+                   int* sorted_entry, int* slot_of_entry, int* active, int* counter, cudaStream_t stream);
 int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
                    const void* w_up, const int* offsets, const int* active, int experts, const float* scores,
-                   void* act, int n_entries, int inter, int hidden, int few_rows, cudaStream_t stream);
+                   void* act, int n_entries, int inter, int hidden, int few_rows, int activation, cudaStream_t stream);
 int hb_moe_down(const void* act, int dtype, const void* w_down, const int* offsets, const int* active, int experts,
                 float* y, int n_entries, int hidden, int inter, int few_rows, cudaStream_t stream);
 
@@ -132,6 +143,19 @@ int hb_delta_recurrence(const float* q, const float* k, const float* v, const fl
                         cudaStream_t stream);   // variant: 0 chosen by sizes, 1 S in shared memory, 16 / 32 rows a lane
 int hb_delta_out_norm(const float* o, const void* gate, int gate_dtype, const void* w, float eps, void* out, int dtype,
                       long long rows, int vdim, cudaStream_t stream);
+
+// mlstm.cu: the matrix memory of the mLSTM (gates and running maximum; S and n token after token; output norm).
+// A request's state row: [heads][vdim + 1][dim] float32 (S column by column, then n), then m [heads] at m_off.
+int hb_mlstm_gates(const float* z, const float* bias_i, const float* bias_f, float cap, float* state,
+                   long long state_stride, long long m_off, const int* cu_seqlens, const int* slots, float* keep,
+                   float* take, float* floor_, int n_seqs, int heads, cudaStream_t stream);
+int hb_mlstm_recurrence(const void* proj, int proj_dtype, long long ld, int q_off, int k_off, int v_off, float q_scale,
+                        const float* keep, const float* take, float* state, long long state_stride,
+                        const int* cu_seqlens, const int* slots, float* o, float* nq, int n_seqs, int heads, int dim,
+                        int vdim, int rows_per_lane, cudaStream_t stream);
+int hb_mlstm_out_norm(const float* o, const float* nq, const float* floor_, const void* proj, int proj_dtype,
+                      long long ld, int g_off, const void* w, int w_dtype, float eps, void* out, int out_dtype,
+                      long long n_tokens, int heads, int vdim, cudaStream_t stream);
 
 // seeded random weights: out[i] = value of element first + i of the tensor with `key` (random_fill.cu)
 int hb_random_normal(void* out, int dtype, long long n, long long first, unsigned long long key, float scale,

@@ -20,7 +20,7 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
                                        int table_stride, const int* __restrict__ seq_of_token,
                                        const int* __restrict__ positions, T* __restrict__ out, int n_tokens,
                                        int nh, int nkv, int hd, int page_size, int chunk, int window,
-                                       float scale, int split_size, int max_splits,
+                                       float scale, int sink, int split_size, int max_splits,
                                        float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ float q_smem[];  // [warps][hd]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -113,6 +113,7 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
     }
     return;
   }
+  if (sink && l > 0.f) l += expf(-m);      // one more term of score 0 in the denominator; it has no value
   const float inv = l > 0.f ? 1.f / l : 0.f;
   T* orow = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
@@ -123,10 +124,10 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
 }
 
 // Combine the splits of each (token, head): o = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m},
-// in split order.
+// in split order. With `sink` the denominator has one more term, e^{0 - m}: a key of score 0 and no value.
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                       T* __restrict__ out, int hd, int max_splits) {
+                                       T* __restrict__ out, int hd, int max_splits, int sink) {
   extern __shared__ float wgt[];   // [max_splits] weight of each split, then 33 floats of scratch
   float* scratch = wgt + max_splits;
   const size_t th = blockIdx.x;
@@ -154,6 +155,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
     l += ml[2 * s + 1] * e;
   }
   l = hb::block_sum(l, scratch);      // fixed tree order: the same inputs give the same sum
+  if (sink && l > 0.f) l += expf(-m);
   const float inv = l > 0.f ? 1.f / l : 0.f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
@@ -182,7 +184,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
 extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                                   const int* block_table, int table_stride, const int* seq_of_token,
                                   const int* positions, void* out, int n_tokens, int nh, int nkv, int hd,
-                                  int page_size, int chunk, int window, float scale, int split_size,
+                                  int page_size, int chunk, int window, float scale, int sink, int split_size,
                                   int max_splits, float* part_acc, float* part_ml, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out) return HB_ERR_BAD_ARG;
   if (max_splits < 1 || (max_splits > 1 && (split_size <= 0 || !part_acc || !part_ml))) return HB_ERR_BAD_ARG;
@@ -200,7 +202,7 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
 #define HB_PAGED_ATTENTION(T, DPL)                                                                              \
   paged_attention_kernel<T, DPL><<<(int)blocks, warps_per_block * 32, smem, stream>>>(                          \
       (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, table_stride, seq_of_token, positions,    \
-      (T*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, split_size, max_splits, part_acc, part_ml)
+      (T*)out, n_tokens, nh, nkv, hd, page_size, chunk, window, scale, sink, split_size, max_splits, part_acc, part_ml)
   if (dtype == HB_DTYPE_F32) {
     if (wide) HB_PAGED_ATTENTION(float, 16); else HB_PAGED_ATTENTION(float, 8);
   } else if (dtype == HB_DTYPE_BF16) {
@@ -212,10 +214,10 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
   HB_LAUNCH_CHECK();
   if (max_splits > 1) {
     if (dtype == HB_DTYPE_F32)
-      attention_merge_kernel<float><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
+      attention_merge_kernel<float><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits, sink);
     else
       attention_merge_kernel<__nv_bfloat16><<<n_tokens * nh, 128, (max_splits + 33) * sizeof(float), stream>>>(
-          part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits);
+          part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits, sink);
     HB_LAUNCH_CHECK();
   }
   return HB_OK;
@@ -223,14 +225,14 @@ extern "C" int hb_paged_attention(const void* q, int dtype, const void* k_pages,
 
 // Merge of split partials alone (the decode kernel writes the same partial layout).
 extern "C" int hb_attention_merge(const float* part_acc, const float* part_ml, void* out, int dtype, int n_rows,
-                                  int hd, int max_splits, cudaStream_t stream) {
+                                  int hd, int max_splits, int sink, cudaStream_t stream) {
   if (!part_acc || !part_ml || !out || n_rows < 0 || hd <= 0 || max_splits < 1) return HB_ERR_BAD_ARG;
   if (n_rows == 0) return HB_OK;
   if (dtype == HB_DTYPE_F32)
-    attention_merge_kernel<float><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits);
+    attention_merge_kernel<float><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(part_acc, part_ml, (float*)out, hd, max_splits, sink);
   else if (dtype == HB_DTYPE_BF16)
     attention_merge_kernel<__nv_bfloat16><<<n_rows, 128, (max_splits + 33) * sizeof(float), stream>>>(
-        part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits);
+        part_acc, part_ml, (__nv_bfloat16*)out, hd, max_splits, sink);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();

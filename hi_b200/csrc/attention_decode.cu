@@ -55,7 +55,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                    int table_stride, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                    __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int chunk, int window,
-                   float scale, int split_size, int max_splits, float* __restrict__ part_acc,
+                   float scale, int sink, int split_size, int max_splits, float* __restrict__ part_acc,
                    float* __restrict__ part_ml) {
   constexpr int STRIDE = HD + 8;                 // padded row: ldmatrix without bank conflicts
   constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
@@ -283,6 +283,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         ml[0] = mx; ml[1] = l;
       }
     } else {
+      if (sink && l > 0.f) l += expf(-mx);     // a key of score 0 without a value
       out[(th0 + row) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
   }
@@ -292,8 +293,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 template <int HD>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                   const int* seq_of_token, const int* positions, void* out, int n_tokens, int nh, int nkv,
-                  int page_size, int chunk, int window, float scale, int split_size, int max_splits, float* part_acc,
-                  float* part_ml, cudaStream_t stream) {
+                  int page_size, int chunk, int window, float scale, int sink, int split_size, int max_splits,
+                  float* part_acc, float* part_ml, cudaStream_t stream) {
   constexpr int STRIDE = HD + 8;
   const size_t smem = (size_t)(ROWS * STRIDE + 4 * TILE * STRIDE) * sizeof(__nv_bfloat16) +
                       (size_t)(NWARPS * ROWS * 2) * sizeof(float);
@@ -303,7 +304,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
   dim3 grid(max_splits, nkv, n_tokens);
   attn_decode_kernel<HD><<<grid, NWARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-      seq_of_token, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, split_size, max_splits,
+      seq_of_token, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, sink, split_size, max_splits,
       part_acc, part_ml);
   HB_LAUNCH_CHECK();
   return HB_OK;
@@ -317,8 +318,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
 extern "C" int hb_attention_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                    int table_stride, const int* seq_of_token, const int* positions, void* out,
                                    int n_tokens, int nh, int nkv, int hd, int page_size, int chunk, int window,
-                                   float scale, int split_size, int max_splits, float* part_acc, float* part_ml,
-                                   cudaStream_t stream) {
+                                   float scale, int sink, int split_size, int max_splits, float* part_acc,
+                                   float* part_ml, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 || chunk < 0 ||
       window < 0 || max_splits < 1 || split_size <= 0 || split_size % TILE != 0)
@@ -328,10 +329,10 @@ extern "C" int hb_attention_decode(const void* q, const void* k_pages, const voi
   if (n_tokens == 0) return HB_OK;
   if (hd == 128)
     return launch_decode<128>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                              nh, nkv, page_size, chunk, window, scale, split_size, max_splits, part_acc, part_ml, stream);
+                              nh, nkv, page_size, chunk, window, scale, sink, split_size, max_splits, part_acc, part_ml, stream);
   if (hd == 64)
     return launch_decode<64>(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                             nh, nkv, page_size, chunk, window, scale, split_size, max_splits, part_acc, part_ml, stream);
+                             nh, nkv, page_size, chunk, window, scale, sink, split_size, max_splits, part_acc, part_ml, stream);
   return HB_ERR_UNSUPPORTED;
 }
 
@@ -405,7 +406,7 @@ extern "C" int hb_attention_decode_static(const void* q, const void* k_pages, co
     if (rc != HB_OK) return rc;
   }
   int rc = hb_attention_decode(q, k_pages, v_pages, block_table, table_stride, seq_of_token, positions, out, n_tokens,
-                               nh, nkv, hd, page_size, chunk, window, scale, split_size, max_splits, acc, ml, stream);
+                               nh, nkv, hd, page_size, chunk, window, scale, 0, split_size, max_splits, acc, ml, stream);
   if (rc != HB_OK || max_splits == 1 || n_tokens == 0) return rc;
-  return hb_attention_merge(acc, ml, out, HB_DTYPE_BF16, n_tokens * nh, hd, max_splits, stream);
+  return hb_attention_merge(acc, ml, out, HB_DTYPE_BF16, n_tokens * nh, hd, max_splits, 0, stream);
 }

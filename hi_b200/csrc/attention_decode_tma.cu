@@ -50,6 +50,7 @@ struct Args {
   int* status;
   int table_stride, nh, nkv, page_size, chunk, split_size, max_splits, box_rows;
   float scale;
+  int sink;      // the softmax's denominator has one more term, e^0: a key of score 0 without a value
 };
 
 // What the fused form needs beside Args.
@@ -443,6 +444,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         ml[0] = mx; ml[1] = l;
       }
     } else {
+      if (a.sink && l > 0.f) l += expf(-mx);
       a.out[(th0 + row) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
   }
@@ -472,6 +474,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       l += l_s[row * n_splits + sp] * e;
     }
     l = hb::warp_sum(l);
+    if (a.sink && l > 0.f) l += expf(-mx);
     if (lane == 0) inv_s[row] = l > 0.f ? 1.f / l : 0.f;
   }
   __syncthreads();
@@ -536,7 +539,7 @@ int launch(const void* k_pages, const void* v_pages, int n_pages, int n_tokens, 
 extern "C" int hb_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                        const int* block_table, int table_stride, const int* seq_of_token,
                                        const int* positions, void* out, int n_tokens, int nh, int nkv, int hd,
-                                       int page_size, int chunk, int window, float scale, int split_size,
+                                       int page_size, int chunk, int window, float scale, int sink, int split_size,
                                        int max_splits, float* part_acc, float* part_ml, int* status,
                                        cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out || !status) return HB_ERR_BAD_ARG;
@@ -550,7 +553,7 @@ extern "C" int hb_attention_decode_tma(const void* q, const void* k_pages, const
   if ((long long)n_pages * nkv * page_size > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;   // row coordinates are 32-bit
   if (n_tokens == 0) return HB_OK;
   Args a{(const __nv_bfloat16*)q, block_table, seq_of_token, positions, (__nv_bfloat16*)out, part_acc, part_ml, status,
-         table_stride, nh, nkv, page_size, chunk, split_size, max_splits, page_size < TILE ? page_size : TILE, scale};
+         table_stride, nh, nkv, page_size, chunk, split_size, max_splits, page_size < TILE ? page_size : TILE, scale, sink};
   const Fuse none{};
   if (hd == 128) return launch<128, false>(k_pages, v_pages, n_pages, n_tokens, a, none, stream);
   if (hd == 64) return launch<64, false>(k_pages, v_pages, n_pages, n_tokens, a, none, stream);
@@ -585,7 +588,7 @@ extern "C" int hb_attention_decode_fused(const void* qkv, const float* inv_freq,
   if ((long long)n_pages * nkv * page_size > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
   if (n_tokens == 0) return HB_OK;
   Args a{nullptr, block_table, seq_of_token, positions, (__nv_bfloat16*)out, part_acc, part_ml, status,
-         table_stride, nh, nkv, page_size, chunk, split_size, max_splits, page_size < TILE ? page_size : TILE, scale};
+         table_stride, nh, nkv, page_size, chunk, split_size, max_splits, page_size < TILE ? page_size : TILE, scale, 0};
   Fuse f{(const __nv_bfloat16*)qkv, inv_freq, rot_pairs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, counters,
          interleaved, qk_norm, temp_on, qk_eps, floor_scale, attn_scale};
   if (hd == 128) return launch<128, true>(k_pages, v_pages, n_pages, n_tokens, a, f, stream);

@@ -23,7 +23,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                     int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                     __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int chunk, int window,
-                    float scale, int skip_single) {
+                    float scale, int skip_single, int sink) {
   constexpr int STRIDE = HD + 8;
   constexpr int CHUNKS = HD / 8;
   constexpr int ROWS_PER_PASS = NWARPS * 32 / CHUNKS;
@@ -205,6 +205,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     }
     __syncthreads();
   }
+  if (sink) {      // one more term of score 0 in the denominator; it has no value
+    if (l_run[0] > 0.f) l_run[0] += expf(-m_run[0]);
+    if (l_run[1] > 0.f) l_run[1] += expf(-m_run[1]);
+  }
   const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
   const float inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
 #pragma unroll
@@ -222,7 +226,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 template <int HD>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                    const int* cu_seqlens, const int* positions, void* out, int n_seqs, int max_new, int nh, int nkv,
-                   int page_size, int chunk, int window, float scale, int skip_single, cudaStream_t stream) {
+                   int page_size, int chunk, int window, float scale, int skip_single, int sink, cudaStream_t stream) {
   constexpr int STRIDE = HD + 8;
   const size_t smem = (size_t)(BQ * STRIDE + 4 * TILE * STRIDE) * sizeof(__nv_bfloat16);
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -230,7 +234,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
   dim3 grid((max_new + BQ - 1) / BQ, nh, n_seqs);
   attn_prefill_kernel<HD><<<grid, NWARPS * 32, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-      cu_seqlens, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, skip_single);
+      cu_seqlens, positions, (__nv_bfloat16*)out, nh, nkv, page_size, chunk, window, scale, skip_single, sink);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -243,7 +247,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
 extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_stride, const int* cu_seqlens, const int* positions, void* out,
                                     int n_seqs, int max_new, int nh, int nkv, int hd, int page_size, int chunk,
-                                    int window, float scale, int skip_single, cudaStream_t stream) {
+                                    int window, float scale, int skip_single, int sink, cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out) return HB_ERR_BAD_ARG;
   if (n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 ||
       chunk < 0 || window < 0)
@@ -252,9 +256,9 @@ extern "C" int hb_attention_prefill(const void* q, const void* k_pages, const vo
   if (n_seqs == 0 || max_new == 0) return HB_OK;
   if (hd == 128)
     return launch_prefill<128>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
-                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, stream);
+                               max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, stream);
   if (hd == 64)
     return launch_prefill<64>(q, k_pages, v_pages, block_table, table_stride, cu_seqlens, positions, out, n_seqs,
-                              max_new, nh, nkv, page_size, chunk, window, scale, skip_single, stream);
+                              max_new, nh, nkv, page_size, chunk, window, scale, skip_single, sink, stream);
   return HB_ERR_UNSUPPORTED;
 }

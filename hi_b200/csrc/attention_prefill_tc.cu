@@ -53,6 +53,7 @@ struct Args {
   int key_splits;
   float* part_acc;
   float* part_ml;
+  int sink;                  // the denominator has one more term, e^0 (a key of score 0 without a value)
 };
 
 template <int HD>
@@ -399,6 +400,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
           }
         } else {
+        if (a.sink && l > 0.f) l += exp2f(-m);         // m is in units of log 2
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* dst = a.out + ((size_t)(tok0 + r) * a.nh + h) * HD;
 #pragma unroll 1
@@ -463,7 +465,7 @@ extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const
                                        int table_stride, const int* cu_seqlens, const int* positions, void* out,
                                        int n_tokens, int n_pages, int n_seqs, int max_new, int nh, int nkv, int hd,
                                        int page_size, int chunk, int window, float scale, int skip_single,
-                                       int key_splits, float* part_acc, float* part_ml, int* status,
+                                       int sink, int key_splits, float* part_acc, float* part_ml, int* status,
                                        cudaStream_t stream) {
   if (!q || !k_pages || !v_pages || !block_table || !cu_seqlens || !positions || !out || !status) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || n_pages <= 0 || n_seqs < 0 || max_new < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 ||
@@ -475,7 +477,7 @@ extern "C" int hb_attention_prefill_tc(const void* q, const void* k_pages, const
   if (!(scale > 0.f)) return HB_ERR_UNSUPPORTED;       // the largest raw score is taken for the largest scaled one
   if (n_seqs == 0 || max_new == 0 || n_tokens == 0) return HB_OK;
   Args a{block_table, cu_seqlens, positions, (__nv_bfloat16*)out, status, table_stride, nh, nkv, page_size, chunk,
-         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml};
+         window, skip_single, page_size < BKEYS ? page_size : BKEYS, scale * 1.4426950408889634f, key_splits, part_acc, part_ml, sink};
   const long long pool_rows = (long long)n_pages * nkv * page_size;
   if (hd == 128) return launch<128>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);
   if (hd == 64) return launch<64>(q, k_pages, v_pages, a, n_tokens, pool_rows, n_seqs, max_new, stream);

@@ -32,37 +32,41 @@ __device__ __forceinline__ void store4_any(void* p, int dtype, size_t i, float4 
   }
 }
 
-// x[t, :] = table[token[t], :]   (crates/hi-mlx/src/models.rs:6206: no multiplier)
+// x[t, :] = table[token[t], :] * scale   (crates/hi-mlx/src/models.rs:6206 has no multiplier: scale 1)
 __global__ void embed_gather_kernel(const void* table, int table_dtype, const int* tokens,
-                                    float* out, int hidden, int vocab) {
+                                    float* out, int hidden, int vocab, float scale) {
   const int t = blockIdx.x;
   int id = tokens[t];
   const bool ok = id >= 0 && id < vocab;
   if ((hidden & 3) == 0) {
 #pragma unroll 4
-    for (int j = threadIdx.x * 4; j < hidden; j += blockDim.x * 4)
-      *reinterpret_cast<float4*>(out + (size_t)t * hidden + j) =
-          ok ? load4_any(table, table_dtype, (size_t)id * hidden + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = threadIdx.x * 4; j < hidden; j += blockDim.x * 4) {
+      float4 v = ok ? load4_any(table, table_dtype, (size_t)id * hidden + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+      *reinterpret_cast<float4*>(out + (size_t)t * hidden + j) = v;
+    }
     return;
   }
   for (int j = threadIdx.x; j < hidden; j += blockDim.x)
-    out[(size_t)t * hidden + j] = ok ? load_any(table, table_dtype, (size_t)id * hidden + j) : 0.f;
+    out[(size_t)t * hidden + j] = ok ? load_any(table, table_dtype, (size_t)id * hidden + j) * scale : 0.f;
 }
 
 // Row r of the output: src = row_map ? row_map[r] : r.
-//   s = x[src] (+ delta[src]);  if no row_map: x[src] = s  (the residual sum, float32)
+//   s = x_scale * x[src] (+ delta[src]);  if no row_map: x[src] = s  (the residual sum, float32)
 //   y[r] = s * rsqrt(mean(s^2) + eps) * w     (crates/hi-cuda/src/kernels.cu:61-77)
+// post != 0 (a block whose norm comes after the sum): the stream takes the normalised row instead of
+// the sum, x[src] = y[r] unrounded.
 __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype, const float* routed,
                                    const int* slot_of_entry, const float* routed_weight, int top_k, const void* w,
                                    int w_dtype, void* y, int y_dtype, float* y_f32, const int* row_map,
-                                   int hidden, float eps) {
+                                   int hidden, float eps, float x_scale, int post) {
   __shared__ float scratch[33];
   extern __shared__ float row[];  // hidden floats
   const int r = blockIdx.x;
   const size_t src = row_map ? (size_t)row_map[r] : (size_t)r;
   float ss = 0.f;
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-    float s = x[src * hidden + j];
+    float s = x[src * hidden + j] * x_scale;
     if (delta) s += load_any(delta, delta_dtype, src * hidden + j);
     if (routed)
       for (int q = 0; q < top_k; ++q)
@@ -74,8 +78,8 @@ __global__ void add_rmsnorm_kernel(float* x, const void* delta, int delta_dtype,
   const float inv = rsqrtf(total / (float)hidden + eps);
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
     const float s = row[j];
-    if (!row_map && (delta || routed)) x[src * hidden + j] = s;
     const float wv = w ? load_any(w, w_dtype, j) : 1.f;
+    if (!row_map && (delta || routed || post)) x[src * hidden + j] = post ? s * inv * wv : s;
     store_any(y, y_dtype, (size_t)r * hidden + j, s * inv * wv);
     if (y_f32) y_f32[(size_t)r * hidden + j] = s * inv * wv;
   }
@@ -91,7 +95,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
                                        const float* __restrict__ routed, const int* __restrict__ slot_of_entry,
                                        const float* __restrict__ routed_weight, int top_k, const void* __restrict__ w, int w_dtype, void* __restrict__ y,
                                        int y_dtype, float* __restrict__ y_f32, const int* __restrict__ row_map,
-                                       int hidden, float eps) {
+                                       int hidden, float eps, float x_scale, int post) {
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const size_t src = row_map ? (size_t)row_map[r] : (size_t)r;
@@ -111,6 +115,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
       // the norm's weight is asked for now, so that it is there when the sum of squares is
       wv[g] = w ? load4_any(w, w_dtype, idx) : make_float4(1.f, 1.f, 1.f, 1.f);
       float4 a = *reinterpret_cast<const float4*>(x + src * hidden + idx);
+      a.x *= x_scale; a.y *= x_scale; a.z *= x_scale; a.w *= x_scale;
       if (delta) {
         const float4 d = load4_any(delta, delta_dtype, src * hidden + idx);
         a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
@@ -132,8 +137,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
     const int idx = (threadIdx.x + g * blockDim.x) * 4;
     if (idx < hidden) {
       const float4 a = v[g];
-      if (!row_map && (delta || routed)) *reinterpret_cast<float4*>(x + src * hidden + idx) = a;
       const float4 o = make_float4(a.x * inv * wv[g].x, a.y * inv * wv[g].y, a.z * inv * wv[g].z, a.w * inv * wv[g].w);
+      if (!row_map && (delta || routed || post)) *reinterpret_cast<float4*>(x + src * hidden + idx) = post ? o : a;
       store4_any(y, y_dtype, (size_t)r * hidden + idx, o);
       if (y_f32) *reinterpret_cast<float4*>(y_f32 + (size_t)r * hidden + idx) = o;
     }
@@ -171,11 +176,11 @@ bool dtype_ok(int d) { return d == HB_DTYPE_F32 || d == HB_DTYPE_BF16; }
 }  // namespace
 
 extern "C" int hb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out,
-                               int n, int hidden, int vocab, cudaStream_t stream) {
+                               int n, int hidden, int vocab, float scale, cudaStream_t stream) {
   if (!table || !tokens || !out || n < 0 || hidden <= 0 || vocab <= 0 || !dtype_ok(table_dtype))
     return HB_ERR_BAD_ARG;
   if (n == 0) return HB_OK;
-  embed_gather_kernel<<<n, 256, 0, stream>>>(table, table_dtype, tokens, out, hidden, vocab);
+  embed_gather_kernel<<<n, 256, 0, stream>>>(table, table_dtype, tokens, out, hidden, vocab, scale);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -200,7 +205,7 @@ extern "C" int hb_feed_tokens(int* tokens, const int* dst, const int* src, const
 extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* routed,
                               const int* slot_of_entry, const float* routed_weight, int top_k, const void* w, int w_dtype, void* y, int y_dtype,
                               float* y_f32, const int* row_map, int rows, int hidden, float eps,
-                              cudaStream_t stream) {
+                              float x_scale, int post, cudaStream_t stream) {
   if (!x || !y || rows < 0 || hidden <= 0 || !dtype_ok(y_dtype) || (delta && !dtype_ok(delta_dtype)) ||
       (w && !dtype_ok(w_dtype)))
     return HB_ERR_BAD_ARG;
@@ -212,7 +217,7 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
     const int ng = (groups + threads - 1) / threads;
 #define HB_NORM_LAUNCH(NG)                                                                                   \
     add_rmsnorm_vec_kernel<NG><<<rows, threads, 0, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, routed_weight, top_k, \
-                                                             w, w_dtype, y, y_dtype, y_f32, row_map, hidden, eps)
+                                                             w, w_dtype, y, y_dtype, y_f32, row_map, hidden, eps, x_scale, post)
     if (ng <= 1) HB_NORM_LAUNCH(1);
     else if (ng <= 2) HB_NORM_LAUNCH(2);
     else if (ng <= 4) HB_NORM_LAUNCH(4);
@@ -229,7 +234,7 @@ extern "C" int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
   }
   const int threads = hidden >= 2048 ? 512 : 256;
   add_rmsnorm_kernel<<<rows, threads, smem, stream>>>(x, delta, delta_dtype, routed, slot_of_entry, routed_weight, top_k, w, w_dtype,
-                                                      y, y_dtype, y_f32, row_map, hidden, eps);
+                                                      y, y_dtype, y_f32, row_map, hidden, eps, x_scale, post);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }
@@ -305,6 +310,45 @@ extern "C" int hb_moe_combine(const float* y, const int* slot_of_entry, const fl
     return HB_ERR_BAD_ARG;
   if (n == 0) return HB_OK;
   moe_combine_kernel<<<n, 256, 0, stream>>>(y, slot_of_entry, routed_weight, shared, shared_dtype, out, hidden, top_k);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+// out = max(in, 0)^2, elementwise; arithmetic in float32; in and out may differ in dtype
+__global__ void relu2_kernel(const void* __restrict__ in, int dtype, void* __restrict__ out, int out_dtype, size_t n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t groups = n / 4;
+  for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    float4 v = load4_any(in, dtype, g * 4);
+    v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+    store4_any(out, out_dtype, g * 4, make_float4(v.x * v.x, v.y * v.y, v.z * v.z, v.w * v.w));
+  }
+  for (size_t i = groups * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float v = fmaxf(load_any(in, dtype, i), 0.f);
+    store_any(out, out_dtype, i, v * v);
+  }
+}
+
+extern "C" int hb_relu2(const void* in, int dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+  if (!in || !out || n < 0 || !dtype_ok(dtype) || !dtype_ok(out_dtype)) return HB_ERR_BAD_ARG;
+  if (n == 0) return HB_OK;
+  const long long want = (n / 4 + 255) / 256 + 1;
+  relu2_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(in, dtype, out, out_dtype, (size_t)n);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+// x <- cap * tanh(x / cap) in place, float32 (a soft limit on the logits)
+__global__ void softcap_kernel(float* __restrict__ x, float cap, float inv_cap, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+extern "C" int hb_softcap(float* x, float cap, long long n, cudaStream_t stream) {
+  if (!x || n < 0 || !(cap > 0.f)) return HB_ERR_BAD_ARG;
+  if (n == 0) return HB_OK;
+  const long long want = (n + 255) / 256;
+  softcap_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(x, cap, 1.f / cap, (size_t)n);
   HB_LAUNCH_CHECK();
   return HB_OK;
 }

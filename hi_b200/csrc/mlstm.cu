@@ -1,0 +1,250 @@
+// The matrix memory of the mLSTM: per head a matrix S [dim, vdim], a vector n [dim] and a running
+// maximum m that every token updates and reads,
+//   i = cap tanh((z_i + b_i) / cap),  f = logsigmoid(cap tanh((z_f + b_f) / cap))
+//   m' = max(f + m, i);  S' = e^(f + m - m') S + e^(i - m') k v^T;  n' = e^(f + m - m') n + e^(i - m') k
+//   o = S'^T q / (max(|n' . q|, e^(-m')) + 1e-6)
+// in three kernels, all float32:
+//   mlstm_gates       the gates' logarithms for all tokens side by side, the scan of m token after token (adds and
+//                     maxima only), then keep = e^(f + m - m'), take = e^(i - m') and floor = e^(-m') side by side
+//   mlstm_recurrence  S and n token after token. n is one more column of S whose value is always 1, so that
+//                     n' . q falls out as one more output. A column lives in the registers of L lanes, R rows each.
+//   mlstm_out_norm    the division, the RMS norm of every head's output, the weight and the sigmoid gate
+// A request's state is one float32 row: [heads][vdim + 1][dim] (column-major S, then n), then m [heads]. It
+// starts at zero, m too.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float load_el(const void* p, int dtype, size_t i) {
+  return dtype == HB_DTYPE_F32 ? reinterpret_cast<const float*>(p)[i]
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+constexpr int GATE_THREADS = 128;
+
+// grid (heads, sequences). z [N, 2 * heads] float32: the input gates' pre-activations, then the forget gates'.
+__global__ void __launch_bounds__(GATE_THREADS)
+mlstm_gates_kernel(const float* __restrict__ z, const float* __restrict__ bias_i, const float* __restrict__ bias_f,
+                   float cap, float* __restrict__ state, long long state_stride, long long m_off,
+                   const int* __restrict__ cu_seqlens, const int* __restrict__ slots, float* __restrict__ keep,
+                   float* __restrict__ take, float* __restrict__ floor_, int heads) {
+  __shared__ float gi[GATE_THREADS], gf[GATE_THREADS], mm[GATE_THREADS + 1];
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int begin = cu_seqlens[seq], end = cu_seqlens[seq + 1];
+  if (begin >= end) return;
+  float* m_state = state + (size_t)slots[seq] * state_stride + m_off + h;
+  const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+  const float inv_cap = 1.f / cap;
+  if (threadIdx.x == 0) mm[0] = *m_state;
+  for (int t0 = begin; t0 < end; t0 += GATE_THREADS) {
+    const int t = t0 + threadIdx.x;
+    const int count = min(GATE_THREADS, end - t0);
+    if (t < end) {
+      const float zi = z[(size_t)t * 2 * heads + h] + bi, zf = z[(size_t)t * 2 * heads + heads + h] + bf;
+      const float ci = cap * tanhf(zi * inv_cap), cf = cap * tanhf(zf * inv_cap);
+      gi[threadIdx.x] = ci;
+      gf[threadIdx.x] = fminf(cf, 0.f) - log1pf(expf(-fabsf(cf)));      // log sigmoid
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = mm[0];
+      for (int j = 0; j < count; ++j) {
+        m = fmaxf(gf[j] + m, gi[j]);
+        mm[j + 1] = m;
+      }
+    }
+    __syncthreads();
+    if (t < end) {
+      const float before = mm[threadIdx.x], now = mm[threadIdx.x + 1];
+      keep[(size_t)t * heads + h] = expf(gf[threadIdx.x] + before - now);
+      take[(size_t)t * heads + h] = expf(gi[threadIdx.x] - now);
+      floor_[(size_t)t * heads + h] = expf(-now);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mm[0] = mm[count];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *m_state = mm[0];
+}
+
+constexpr int REC_THREADS = 256;
+constexpr int REC_TOKENS = 8;      // tokens staged in shared memory at a time
+
+// grid (column groups, heads, sequences); a block holds REC_THREADS / L columns of one head's S (column vdim is n).
+// Lane l of a column's L lanes holds rows l * R .. l * R + R - 1. Rows past dim hold zeros and meet zeros.
+template <int R>
+__global__ void __launch_bounds__(REC_THREADS)
+mlstm_recurrence_kernel(const void* __restrict__ proj, int proj_dtype, long long ld, int q_off, int k_off, int v_off,
+                        float q_scale, const float* __restrict__ keep, const float* __restrict__ take,
+                        float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
+                        const int* __restrict__ slots, float* __restrict__ o, float* __restrict__ nq, int heads,
+                        int dim, int vdim, int L) {
+  extern __shared__ float sm[];       // per staged token: q [dim_pad], k [dim_pad], v [cols], keep, take
+  const int h = blockIdx.y, seq = blockIdx.z;
+  const int begin = cu_seqlens[seq], end = cu_seqlens[seq + 1];
+  if (begin >= end) return;
+  const int cols_per_block = REC_THREADS / L;
+  const int dim_pad = L * R;
+  const int col0 = blockIdx.x * cols_per_block;
+  const int col = col0 + threadIdx.x / L;          // my column; vdim = the column of n
+  const int sub = threadIdx.x % L;
+  const bool live = col <= vdim;
+  const int per_token = 2 * dim_pad + cols_per_block + 2;
+  float* S_col = state + (size_t)slots[seq] * state_stride + ((size_t)h * (vdim + 1) + (live ? col : 0)) * dim;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int d = sub * R + r;
+    S[r] = (live && d < dim) ? S_col[d] : 0.f;
+  }
+  for (int t0 = begin; t0 < end; t0 += REC_TOKENS) {
+    const int count = min(REC_TOKENS, end - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < count * dim_pad; i += REC_THREADS) {
+      const int j = i / dim_pad, d = i - j * dim_pad;
+      const size_t row = (size_t)(t0 + j) * ld + (size_t)h * dim + d;
+      float* dst = sm + j * per_token;
+      dst[d] = d < dim ? load_el(proj, proj_dtype, row + q_off) * q_scale : 0.f;
+      dst[dim_pad + d] = d < dim ? load_el(proj, proj_dtype, row + k_off) : 0.f;
+    }
+    for (int i = threadIdx.x; i < count * (cols_per_block + 2); i += REC_THREADS) {
+      const int j = i / (cols_per_block + 2), c = i - j * (cols_per_block + 2);
+      float* dst = sm + j * per_token + 2 * dim_pad;
+      if (c < cols_per_block) {
+        const int cc = col0 + c;
+        dst[c] = cc < vdim ? load_el(proj, proj_dtype, (size_t)(t0 + j) * ld + v_off + (size_t)h * vdim + cc)
+                           : (cc == vdim ? 1.f : 0.f);
+      } else {
+        dst[c] = (c == cols_per_block ? keep : take)[(size_t)(t0 + j) * heads + h];
+      }
+    }
+    __syncthreads();
+    for (int j = 0; j < count; ++j) {
+      const float* tok = sm + j * per_token;
+      const float* qs = tok + sub * R;
+      const float* ks = tok + dim_pad + sub * R;
+      const float a = tok[2 * dim_pad + cols_per_block];
+      const float bv = tok[2 * dim_pad + cols_per_block + 1] * tok[2 * dim_pad + threadIdx.x / L];
+      float acc = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        S[r] = fmaf(bv, ks[r], a * S[r]);
+        acc = fmaf(S[r], qs[r], acc);
+      }
+      for (int off = L >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (sub == 0 && live) {
+        if (col < vdim) o[((size_t)(t0 + j) * heads + h) * vdim + col] = acc;
+        else nq[(size_t)(t0 + j) * heads + h] = acc;
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int d = sub * R + r;
+      if (d < dim) S_col[d] = S[r];
+    }
+  }
+}
+
+// One warp per (token, head): h_j = o_j / (max(|n.q|, floor) + 1e-6); y = h / sqrt(mean h^2 + eps) * w[head, j]
+// * sigmoid(gate[token, head, j]); the gate is a column run of `proj`.
+__global__ void mlstm_out_norm_kernel(const float* __restrict__ o, const float* __restrict__ nq,
+                                      const float* __restrict__ floor_, const void* __restrict__ proj, int proj_dtype,
+                                      long long ld, int g_off, const void* __restrict__ w, int w_dtype, float eps,
+                                      void* __restrict__ out, int out_dtype, long long rows, int heads, int vdim) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = row / heads;
+  const int h = (int)(row - t * heads);
+  const float den = 1.f / (fmaxf(fabsf(nq[row]), floor_[row]) + 1e-6f);
+  const float* orow = o + row * vdim;
+  float ss = 0.f;
+  for (int j = lane; j < vdim; j += 32) {
+    const float v = orow[j] * den;
+    ss += v * v;
+  }
+  ss = hb::warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)vdim + eps) * den;
+  for (int j = lane; j < vdim; j += 32) {
+    const float g = load_el(proj, proj_dtype, (size_t)t * ld + g_off + (size_t)h * vdim + j);
+    const float y = orow[j] * inv * load_el(w, w_dtype, (size_t)h * vdim + j) / (1.f + expf(-g));
+    if (out_dtype == HB_DTYPE_F32) reinterpret_cast<float*>(out)[row * vdim + j] = y;
+    else reinterpret_cast<__nv_bfloat16*>(out)[row * vdim + j] = __float2bfloat16_rn(y);
+  }
+}
+
+bool dtype_ok(int d) { return d == HB_DTYPE_F32 || d == HB_DTYPE_BF16; }
+
+}  // namespace
+
+extern "C" int hb_mlstm_gates(const float* z, const float* bias_i, const float* bias_f, float cap, float* state,
+                              long long state_stride, long long m_off, const int* cu_seqlens, const int* slots,
+                              float* keep, float* take, float* floor_, int n_seqs, int heads, cudaStream_t stream) {
+  if (!z || !state || !cu_seqlens || !slots || !keep || !take || !floor_ || n_seqs < 0 || heads <= 0 || !(cap > 0.f))
+    return HB_ERR_BAD_ARG;
+  if (n_seqs == 0) return HB_OK;
+  if (n_seqs > 65535) return HB_ERR_UNSUPPORTED;
+  mlstm_gates_kernel<<<dim3(heads, n_seqs), GATE_THREADS, 0, stream>>>(z, bias_i, bias_f, cap, state, state_stride, m_off,
+                                                                        cu_seqlens, slots, keep, take, floor_, heads);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+// rows_per_lane: 0 = chosen by dim (4 up to 128, 8 up to 256, 16 up to 512, 32 up to 1024), or one of 4, 8, 16, 32
+// (the sums over a column's rows then run in another order: results move by rounding).
+extern "C" int hb_mlstm_recurrence(const void* proj, int proj_dtype, long long ld, int q_off, int k_off, int v_off,
+                                   float q_scale, const float* keep, const float* take, float* state,
+                                   long long state_stride, const int* cu_seqlens, const int* slots, float* o, float* nq,
+                                   int n_seqs, int heads, int dim, int vdim, int rows_per_lane, cudaStream_t stream) {
+  if (!proj || !keep || !take || !state || !cu_seqlens || !slots || !o || !nq || n_seqs < 0 || heads <= 0 || dim <= 0 ||
+      vdim <= 0 || !dtype_ok(proj_dtype))
+    return HB_ERR_BAD_ARG;
+  if (n_seqs == 0) return HB_OK;
+  if (dim > 1024 || n_seqs > 65535 || heads > 65535) return HB_ERR_UNSUPPORTED;
+  int R = rows_per_lane;
+  if (R == 0) R = dim <= 128 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
+  if (!(R == 4 || R == 8 || R == 16 || R == 32) || 32 * R < dim) return HB_ERR_BAD_ARG;
+  int L = 1;
+  while (L * R < dim) L *= 2;
+  const int cols_per_block = REC_THREADS / L;
+  const dim3 grid((vdim + 1 + cols_per_block - 1) / cols_per_block, heads, n_seqs);
+  const size_t smem = (size_t)REC_TOKENS * (2 * L * R + cols_per_block + 2) * sizeof(float);
+#define HB_MLSTM_REC(RR)                                                                                          \
+  do {                                                                                                            \
+    if (smem > 48 * 1024) {                                                                                       \
+      cudaError_t e = cudaFuncSetAttribute(mlstm_recurrence_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem);                                                            \
+      if (e != cudaSuccess) return (int)e;                                                                        \
+    }                                                                                                             \
+    mlstm_recurrence_kernel<RR><<<grid, REC_THREADS, smem, stream>>>(proj, proj_dtype, ld, q_off, k_off, v_off,    \
+                                                                     q_scale, keep, take, state, state_stride,    \
+                                                                     cu_seqlens, slots, o, nq, heads, dim, vdim, L); \
+  } while (0)
+  if (R == 4) HB_MLSTM_REC(4);
+  else if (R == 8) HB_MLSTM_REC(8);
+  else if (R == 16) HB_MLSTM_REC(16);
+  else HB_MLSTM_REC(32);
+#undef HB_MLSTM_REC
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
+extern "C" int hb_mlstm_out_norm(const float* o, const float* nq, const float* floor_, const void* proj, int proj_dtype,
+                                 long long ld, int g_off, const void* w, int w_dtype, float eps, void* out,
+                                 int out_dtype, long long n_tokens, int heads, int vdim, cudaStream_t stream) {
+  if (!o || !nq || !floor_ || !proj || !w || !out || n_tokens < 0 || heads <= 0 || vdim <= 0 || !dtype_ok(proj_dtype) ||
+      !dtype_ok(w_dtype) || !dtype_ok(out_dtype))
+    return HB_ERR_BAD_ARG;
+  const long long rows = n_tokens * heads;
+  if (rows == 0) return HB_OK;
+  const int warps = 8;
+  const long long blocks = (rows + warps - 1) / warps;
+  if (blocks > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
+  mlstm_out_norm_kernel<<<(int)blocks, warps * 32, 0, stream>>>(o, nq, floor_, proj, proj_dtype, ld, g_off, w, w_dtype, eps,
+                                                               out, out_dtype, rows, heads, vdim);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}

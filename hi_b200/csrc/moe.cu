@@ -160,24 +160,48 @@ __device__ __forceinline__ void router_part_range(int hidden, int part, int& run
 // was written by other blocks of this launch and is read past L1. `mode`: bit 0 clear = the sigmoid
 // of the chosen logit (crates/hi-mlx/src/models.rs:6090), set = its softmax over all experts
 // (the donor kernel's two scoring rules: crates/hi-cuda/src/kernels.cu:536-546); bit 1 = the chosen
-// scores are divided by their sum.
+// scores are divided by their sum. Bits 8-15 = G and 16-23 = KEEP, G > 0: the experts lie in G equal groups of
+// neighbours, a group counts as the sum of the two largest sigmoids of its logits (the largest, if it has one
+// expert), and only experts of the KEEP best groups (ties to the lower group) can be chosen.
 constexpr int ROUTER_SOFTMAX = 1, ROUTER_RENORMALIZE = 2;
+constexpr int ROUTER_MAX_GROUPS = 64;
 
 template <bool THROUGH_L2 = false>
-__device__ __forceinline__ void router_select(const float* row, int experts, int top_k, int mode, int* ids,
-                                              float* scores) {
+__device__ __forceinline__ void router_select(const float* row, int experts, int top_k, int mode, float score_scale,
+                                              int* ids, float* scores) {
   float mx = -INFINITY, denom = 1.f;
   if (mode & ROUTER_SOFTMAX) {
     for (int e = 0; e < experts; ++e) mx = fmaxf(mx, THROUGH_L2 ? __ldcg(row + e) : row[e]);
     denom = 0.f;
     for (int e = 0; e < experts; ++e) denom += expf((THROUGH_L2 ? __ldcg(row + e) : row[e]) - mx);
   }
+  const int groups = (mode >> 8) & 0xff, keep = (mode >> 16) & 0xff;
+  const int per = groups > 0 ? experts / groups : experts;
+  unsigned long long open = ~0ull;           // bit g: experts of group g can be chosen
+  if (groups > 0 && keep < groups) {
+    open = 0ull;
+    for (int r = 0; r < keep; ++r) {
+      int best = -1;
+      float bv = 0.f;
+      for (int g = 0; g < groups; ++g) {
+        if ((open >> g) & 1ull) continue;
+        float a = -INFINITY, b = -INFINITY;  // the two largest logits of the group
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = THROUGH_L2 ? __ldcg(row + e) : row[e];
+          if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+        }
+        const float sum = 1.f / (1.f + expf(-a)) + (per > 1 ? 1.f / (1.f + expf(-b)) : 0.f);
+        if (best < 0 || sum > bv) { best = g; bv = sum; }
+      }
+      open |= 1ull << best;
+    }
+  }
   float chosen = 0.f;
   for (int r = 0; r < top_k; ++r) {
     int best = -1;
     float bv = 0.f;
     for (int e = 0; e < experts; ++e) {
-      bool taken = false;
+      bool taken = groups > 0 && !((open >> (e / per)) & 1ull);
       for (int q = 0; q < r; ++q) taken |= (ids[q] == e);
       if (taken) continue;
       const float v = THROUGH_L2 ? __ldcg(row + e) : row[e];
@@ -189,6 +213,8 @@ __device__ __forceinline__ void router_select(const float* row, int experts, int
   }
   if (mode & ROUTER_RENORMALIZE)
     for (int r = 0; r < top_k; ++r) scores[r] /= chosen;
+  if (score_scale != 1.f)
+    for (int r = 0; r < top_k; ++r) scores[r] *= score_scale;     // a constant factor on every weight
 }
 
 // Few tokens: a block takes one token and ROUTER_FEW_EXP experts, a warp one part of K of one
@@ -201,7 +227,7 @@ constexpr int ROUTER_FEW_EXP = 4;
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(ROUTER_FEW_EXP * ROUTER_KPARTS * 32)
 router_few_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int n, int hidden, int experts, int top_k,
-                  int mode, float* logits, int* ids, float* scores, int* __restrict__ offsets,
+                  int mode, float score_scale, float* logits, int* ids, float* scores, int* __restrict__ offsets,
                   int* __restrict__ sorted_entry, int* __restrict__ slot_of_entry, int* __restrict__ active,
                   int* counter) {
   __shared__ float partial[ROUTER_FEW_EXP][ROUTER_KPARTS];
@@ -272,7 +298,8 @@ router_few_kernel(const TX* __restrict__ x, const TW* __restrict__ w, int n, int
   int* s_ids = plan_scratch + 2 * experts;          // [n * top_k]
   for (int tok = threadIdx.x; tok < n; tok += blockDim.x) {
     int* mine = s_ids + tok * top_k;
-    router_select<true>(logits + (size_t)tok * experts, experts, top_k, mode, mine, scores + (size_t)tok * top_k);
+    router_select<true>(logits + (size_t)tok * experts, experts, top_k, mode, score_scale, mine,
+                        scores + (size_t)tok * top_k);
     for (int r = 0; r < top_k; ++r) ids[(size_t)tok * top_k + r] = mine[r];
   }
   __syncthreads();
@@ -290,7 +317,7 @@ constexpr int ROUTER_TOK = 4, ROUTER_EXP = 16;
 template <typename TW>
 __global__ void __launch_bounds__(ROUTER_KPARTS * 32)
 router_logits_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w, int n, int hidden, int experts,
-                           int top_k, int mode, float* __restrict__ logits, int* __restrict__ ids,
+                           int top_k, int mode, float score_scale, float* __restrict__ logits, int* __restrict__ ids,
                            float* __restrict__ scores) {
   __shared__ float partial[ROUTER_KPARTS][ROUTER_TOK][ROUTER_EXP];
   __shared__ float lg[ROUTER_TOK][ROUTER_EXP];
@@ -359,15 +386,16 @@ router_logits_tiled_kernel(const float* __restrict__ x, const TW* __restrict__ w
   __syncthreads();
   if (threadIdx.x < ROUTER_TOK && t0 + threadIdx.x < n) {
     const size_t t = t0 + threadIdx.x;
-    router_select(lg[threadIdx.x], experts, top_k, mode, ids + t * top_k, scores + t * top_k);
+    router_select(lg[threadIdx.x], experts, top_k, mode, score_scale, ids + t * top_k, scores + t * top_k);
   }
 }
 
 // Selection from stored logits, one thread per token (more experts than one block column holds).
 __global__ void router_select_kernel(const float* __restrict__ logits, int n, int experts, int top_k, int mode,
-                                     int* __restrict__ ids, float* __restrict__ scores) {
+                                     float score_scale, int* __restrict__ ids, float* __restrict__ scores) {
   const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < (size_t)n) router_select(logits + t * experts, experts, top_k, mode, ids + t * top_k, scores + t * top_k);
+  if (t < (size_t)n)
+    router_select(logits + t * experts, experts, top_k, mode, score_scale, ids + t * top_k, scores + t * top_k);
 }
 
 // ------------------------------------------------------------------ plan
@@ -393,17 +421,19 @@ int launch_plan(const int* ids, int n, int experts, int* offsets, int* sorted_en
 
 // ------------------------------------------------------------------ grouped products, general form
 // C[r, n] = sum_k A[row(r), k] * W[e(r), n, k] for the sorted slots r of every expert e.
-// DUAL: two weight stacks (gate, up); out = silu(s*g) * (s*u) in the engine dtype.
-// else: out = float32 product (the down projection).
+// MODE 1 (DUAL): two weight stacks (gate, up); out = silu(s*g) * (s*u) in the engine dtype.
+// MODE 2: one stack; out = max(s*u, 0)^2 in the engine dtype (an expert without a gate branch).
+// MODE 0: out = float32 product (the down projection).
 // Tiles BM x BN over (expert, rows of that expert) x columns; any K, any number of columns.
 constexpr int BM = 32, BN = 64, BK = 16, GT = 256;
 
-template <typename T, bool DUAL>
+template <typename T, int MODE>
 __global__ void grouped_gemm_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry,
                                     int top_k, const T* __restrict__ W0, const T* __restrict__ W1,
                                     const int* __restrict__ offsets, int experts,
                                     const float* __restrict__ scores, void* __restrict__ out, int n_out,
                                     int K) {
+  constexpr bool DUAL = MODE == 1;
   __shared__ float As[BK][BM + 1];
   __shared__ float Bs0[BK][BN + 1];
   __shared__ float Bs1[DUAL ? BK : 1][BN + 1];
@@ -478,7 +508,7 @@ __global__ void grouped_gemm_kernel(const T* __restrict__ A, int lda, const int*
     if (r >= rows) continue;
     const int slot = row0 + r;
     float s = 1.f;
-    if (DUAL) s = scores[sorted_entry ? sorted_entry[slot] : slot];
+    if (MODE != 0) s = scores[sorted_entry ? sorted_entry[slot] : slot];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int n = col0 + tn * 4 + c;
@@ -486,6 +516,9 @@ __global__ void grouped_gemm_kernel(const T* __restrict__ A, int lda, const int*
       if (DUAL) {
         const float g = s * acc0[rr][c], u = s * acc1[rr][c];
         reinterpret_cast<T*>(out)[(size_t)slot * n_out + n] = hb::from_f32<T>(g / (1.f + expf(-g)) * u);
+      } else if (MODE == 2) {
+        const float u = fmaxf(s * acc0[rr][c], 0.f);
+        reinterpret_cast<T*>(out)[(size_t)slot * n_out + n] = hb::from_f32<T>(u * u);
       } else {
         reinterpret_cast<float*>(out)[(size_t)slot * n_out + n] = acc0[rr][c];
       }
@@ -500,13 +533,14 @@ __global__ void grouped_gemm_kernel(const T* __restrict__ A, int lda, const int*
 constexpr int RMAX = 8;
 constexpr int GEMV_WARPS = 8;
 
-template <typename T, bool DUAL, int R>
+template <typename T, int MODE, int R>
 __device__ __forceinline__ void gemv_rows(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry,
                                           int top_k, const T* __restrict__ w0, const T* __restrict__ w1,
                                           const float* __restrict__ scores, void* __restrict__ out, int n_out,
                                           int K, int n, int r0, int lane) {
   // gate/up streams two weight rows per lane; the down projection has one, and needs twice the
   // unroll for as many bytes in flight (measured at three blocks per SM: 4 and 8 beat 2, 3 or 8 and 4 or 16)
+  constexpr bool DUAL = MODE == 1;
   constexpr int GEMV_UNROLL = DUAL ? 4 : 8;
   const T* arow[R];
   float sc[R];
@@ -515,7 +549,7 @@ __device__ __forceinline__ void gemv_rows(const T* __restrict__ A, int lda, cons
     const int slot = r0 + r;
     const size_t ar = sorted_entry ? (size_t)(sorted_entry[slot] / top_k) : (size_t)slot;
     arow[r] = A + ar * lda;
-    sc[r] = DUAL ? scores[sorted_entry ? sorted_entry[slot] : slot] : 1.f;
+    sc[r] = MODE != 0 ? scores[sorted_entry ? sorted_entry[slot] : slot] : 1.f;
   }
   float g[R], u[R];
 #pragma unroll
@@ -558,6 +592,9 @@ __device__ __forceinline__ void gemv_rows(const T* __restrict__ A, int lda, cons
       if (DUAL) {
         const float gg = sc[r] * gs, uu = sc[r] * us;
         reinterpret_cast<T*>(out)[o] = hb::from_f32<T>(gg / (1.f + expf(-gg)) * uu);
+      } else if (MODE == 2) {
+        const float uu = fmaxf(sc[r] * gs, 0.f);
+        reinterpret_cast<T*>(out)[o] = hb::from_f32<T>(uu * uu);
       } else {
         reinterpret_cast<float*>(out)[o] = gs;
       }
@@ -565,7 +602,7 @@ __device__ __forceinline__ void gemv_rows(const T* __restrict__ A, int lda, cons
   }
 }
 
-template <typename T, bool DUAL>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(GEMV_WARPS * 32, 3)   // three blocks per SM (measured: +5 % on the batch-8 step over two)
 grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted_entry, int top_k,
                     const T* __restrict__ W0, const T* __restrict__ W1, const int* __restrict__ offsets,
@@ -580,48 +617,54 @@ grouped_gemv_kernel(const T* __restrict__ A, int lda, const int* __restrict__ so
   const int n = blockIdx.x * GEMV_WARPS + warp;
   if (n >= n_out) return;
   const T* w0 = W0 + ((size_t)e * n_out + n) * K;
-  const T* w1 = DUAL ? W1 + ((size_t)e * n_out + n) * K : nullptr;
+  const T* w1 = MODE == 1 ? W1 + ((size_t)e * n_out + n) * K : nullptr;
   int r0 = begin;
   // rows in runs of 8, 4, 2, 1: every row count is covered, each weight element is reused by
   // the whole run
   for (; r0 + 8 <= end; r0 += 8)
-    gemv_rows<T, DUAL, 8>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
+    gemv_rows<T, MODE, 8>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
   if (r0 + 4 <= end) {
-    gemv_rows<T, DUAL, 4>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
+    gemv_rows<T, MODE, 4>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
     r0 += 4;
   }
   if (r0 + 2 <= end) {
-    gemv_rows<T, DUAL, 2>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
+    gemv_rows<T, MODE, 2>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
     r0 += 2;
   }
-  if (r0 < end) gemv_rows<T, DUAL, 1>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
+  if (r0 < end) gemv_rows<T, MODE, 1>(A, lda, sorted_entry, top_k, w0, w1, scores, out, n_out, K, n, r0, lane);
 }
 
-template <typename T>
-int launch_grouped(bool dual, const void* A, int lda, const int* sorted_entry, int top_k, const void* W0,
-                   const void* W1, const int* offsets, const int* active, int experts, const float* scores, void* out,
-                   int n_entries, int n_out, int K, int few_rows, cudaStream_t stream) {
+template <typename T, int MODE>
+int launch_grouped_mode(const void* A, int lda, const int* sorted_entry, int top_k, const void* W0, const void* W1,
+                        const int* offsets, const int* active, int experts, const float* scores, void* out,
+                        int n_entries, int n_out, int K, int few_rows, cudaStream_t stream) {
   if (few_rows && K % 8 == 0 && lda % 8 == 0) {
     dim3 grid((n_out + GEMV_WARPS - 1) / GEMV_WARPS, experts < n_entries ? experts : n_entries);
-    if (dual)
-      grouped_gemv_kernel<T, true><<<grid, GEMV_WARPS * 32, 0, stream>>>(
-          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, (const T*)W1, offsets, active, scores, out, n_out, K);
-    else
-      grouped_gemv_kernel<T, false><<<grid, GEMV_WARPS * 32, 0, stream>>>(
-          (const T*)A, lda, sorted_entry, top_k, (const T*)W0, nullptr, offsets, active, scores, out, n_out, K);
+    grouped_gemv_kernel<T, MODE><<<grid, GEMV_WARPS * 32, 0, stream>>>(
+        (const T*)A, lda, sorted_entry, top_k, (const T*)W0, (const T*)W1, offsets, active, scores, out, n_out, K);
   } else {
     const int max_tiles = (n_entries + BM - 1) / BM + (experts < n_entries ? experts : n_entries);
     dim3 grid((n_out + BN - 1) / BN, max_tiles);
     if (grid.y > 65535) return HB_ERR_UNSUPPORTED;
-    if (dual)
-      grouped_gemm_kernel<T, true><<<grid, GT, 0, stream>>>((const T*)A, lda, sorted_entry, top_k, (const T*)W0,
-                                                            (const T*)W1, offsets, experts, scores, out, n_out, K);
-    else
-      grouped_gemm_kernel<T, false><<<grid, GT, 0, stream>>>((const T*)A, lda, sorted_entry, top_k, (const T*)W0,
-                                                             nullptr, offsets, experts, scores, out, n_out, K);
+    grouped_gemm_kernel<T, MODE><<<grid, GT, 0, stream>>>((const T*)A, lda, sorted_entry, top_k, (const T*)W0,
+                                                          (const T*)W1, offsets, experts, scores, out, n_out, K);
   }
   HB_LAUNCH_CHECK();
   return HB_OK;
+}
+
+// mode: 0 float32 product, 1 gate/up with SwiGLU, 2 one stack with the squared relu
+template <typename T>
+int launch_grouped(int mode, const void* A, int lda, const int* sorted_entry, int top_k, const void* W0,
+                   const void* W1, const int* offsets, const int* active, int experts, const float* scores, void* out,
+                   int n_entries, int n_out, int K, int few_rows, cudaStream_t stream) {
+#define HB_GROUPED(M)                                                                                              \
+  launch_grouped_mode<T, M>(A, lda, sorted_entry, top_k, W0, M == 1 ? W1 : nullptr, offsets, active, experts, scores, \
+                            out, n_entries, n_out, K, few_rows, stream)
+  if (mode == 1) return HB_GROUPED(1);
+  if (mode == 2) return HB_GROUPED(2);
+  return HB_GROUPED(0);
+#undef HB_GROUPED
 }
 
 }  // namespace
@@ -631,11 +674,17 @@ namespace {
 // The router, and with `counter` (an int that is zero between launches) the plan as well: in the
 // same kernel when a block takes one token, by the plan's own kernel after the tiled one.
 int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts, int top_k, int mode,
-                  float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
+                  float score_scale, float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry, int* slot_of_entry,
                   int* active, int* counter, cudaStream_t stream) {
   if (!x || !w || !ids || !scores || n < 0 || hidden <= 0 || experts <= 0 || top_k <= 0 || top_k > experts || mode < 0 ||
-      mode > 3)
+      (mode & 0xff) > 3 || (mode >> 24) != 0)
     return HB_ERR_BAD_ARG;
+  {
+    const int groups = (mode >> 8) & 0xff, keep = (mode >> 16) & 0xff;
+    if (groups > ROUTER_MAX_GROUPS) return HB_ERR_UNSUPPORTED;
+    if (groups > 0 && (experts % groups != 0 || keep < 1 || keep > groups || top_k > keep * (experts / groups)))
+      return HB_ERR_BAD_ARG;
+  }
   if (experts > 4096) return HB_ERR_UNSUPPORTED;
   if (n == 0) return HB_OK;
   if (x_dtype == HB_DTYPE_F32 && n >= 96 && hidden % 8 == 0 && (w_dtype == HB_DTYPE_F32 || w_dtype == HB_DTYPE_BF16)) {
@@ -647,13 +696,13 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
     if (grid.y > 65535) return HB_ERR_UNSUPPORTED;
     if (w_dtype == HB_DTYPE_F32)
       router_logits_tiled_kernel<float><<<grid, ROUTER_KPARTS * 32, 0, stream>>>(
-          (const float*)x, (const float*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores);
+          (const float*)x, (const float*)w, n, hidden, experts, top_k, mode, score_scale, logits_out, ids, scores);
     else
       router_logits_tiled_kernel<__nv_bfloat16><<<grid, ROUTER_KPARTS * 32, 0, stream>>>(
-          (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores);
+          (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, score_scale, logits_out, ids, scores);
     HB_LAUNCH_CHECK();
     if (grid.y > 1) {
-      router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, mode, ids, scores);
+      router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, mode, score_scale, ids, scores);
       HB_LAUNCH_CHECK();
     }
     if (counter) {
@@ -673,21 +722,21 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
   const dim3 grid(n, columns);
   if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_F32)
     router_few_kernel<float, float><<<grid, threads, smem, stream>>>(
-        (const float*)x, (const float*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets, sorted_entry,
-        slot_of_entry, active, fused);
+        (const float*)x, (const float*)w, n, hidden, experts, top_k, mode, score_scale, logits_out, ids, scores, offsets,
+        sorted_entry, slot_of_entry, active, fused);
   else if (x_dtype == HB_DTYPE_F32 && w_dtype == HB_DTYPE_BF16)
     router_few_kernel<float, __nv_bfloat16><<<grid, threads, smem, stream>>>(
-        (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets,
-        sorted_entry, slot_of_entry, active, fused);
+        (const float*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, score_scale, logits_out, ids, scores,
+        offsets, sorted_entry, slot_of_entry, active, fused);
   else if (x_dtype == HB_DTYPE_BF16 && w_dtype == HB_DTYPE_BF16)
     router_few_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, smem, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets,
-        sorted_entry, slot_of_entry, active, fused);
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, n, hidden, experts, top_k, mode, score_scale, logits_out, ids, scores,
+        offsets, sorted_entry, slot_of_entry, active, fused);
   else
     return HB_ERR_BAD_ARG;
   HB_LAUNCH_CHECK();
   if (!fused) {
-    router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, mode, ids, scores);
+    router_select_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits_out, n, experts, top_k, mode, score_scale, ids, scores);
     HB_LAUNCH_CHECK();
     if (counter) {
       if (int rc = launch_plan(ids, n * top_k, experts, offsets, sorted_entry, slot_of_entry, active, stream)) return rc;
@@ -699,23 +748,24 @@ int router_launch(const void* x, int x_dtype, const void* w, int w_dtype, int n,
 }  // namespace
 
 extern "C" int hb_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden,
-                              int experts, int top_k, int mode, float* logits_out, int* ids, float* scores,
-                              cudaStream_t stream) {
-  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, mode, logits_out, ids, scores, nullptr, nullptr,
+                              int experts, int top_k, int mode, float score_scale, float* logits_out, int* ids,
+                              float* scores, cudaStream_t stream) {
+  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, mode, score_scale, logits_out, ids, scores, nullptr, nullptr,
                        nullptr, nullptr, nullptr, stream);
 }
 
 // Router and plan in one call; `counter` is one int that the caller zeroed once and then leaves alone.
 extern "C" int hb_router_plan(const void* x, int x_dtype, const void* w, int w_dtype, int n, int hidden, int experts,
-                              int top_k, int mode, float* logits_out, int* ids, float* scores, int* offsets, int* sorted_entry,
-                              int* slot_of_entry, int* active, int* counter, cudaStream_t stream) {
+                              int top_k, int mode, float score_scale, float* logits_out, int* ids, float* scores,
+                              int* offsets, int* sorted_entry, int* slot_of_entry, int* active, int* counter,
+                              cudaStream_t stream) {
   if (!offsets || !sorted_entry || !slot_of_entry || !active || !counter) return HB_ERR_BAD_ARG;
   if (experts <= 0 || experts > 4096) return experts <= 0 ? HB_ERR_BAD_ARG : HB_ERR_UNSUPPORTED;
   if (n == 0) {  // nothing routed: an empty plan
     return launch_plan(ids, 0, experts, offsets, sorted_entry, slot_of_entry, active, stream);
   }
-  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, mode, logits_out, ids, scores, offsets,
-                       sorted_entry, slot_of_entry, active, counter, stream);
+  return router_launch(x, x_dtype, w, w_dtype, n, hidden, experts, top_k, mode, score_scale, logits_out, ids, scores,
+                       offsets, sorted_entry, slot_of_entry, active, counter, stream);
 }
 
 extern "C" int hb_moe_plan(const int* ids, int n_entries, int experts, int* offsets, int* sorted_entry,
@@ -726,21 +776,25 @@ extern "C" int hb_moe_plan(const int* ids, int n_entries, int experts, int* offs
   return launch_plan(ids, n_entries, experts, offsets, sorted_entry, slot_of_entry, active, stream);
 }
 
-// gate/up with SwiGLU: act[slot, :] (engine dtype, [n_entries, inter]).
+// gate/up with SwiGLU: act[slot, :] (engine dtype, [n_entries, inter]). activation 1: experts without a gate
+// branch, act = max(s * x Wu^T, 0)^2 (w_gate is not read).
 extern "C" int hb_moe_gate_up(const void* x, int dtype, const int* sorted_entry, int top_k, const void* w_gate,
                               const void* w_up, const int* offsets, const int* active, int experts,
                               const float* scores, void* act, int n_entries, int inter, int hidden, int few_rows,
-                              cudaStream_t stream) {
+                              int activation, cudaStream_t stream) {
+  if (activation != 0 && activation != 1) return HB_ERR_BAD_ARG;
+  if (activation == 1) w_gate = w_up;
+  const int mode = activation == 1 ? 2 : 1;
   if (!x || !sorted_entry || !w_gate || !w_up || !offsets || !active || !scores || !act || n_entries < 0 || inter <= 0 ||
       hidden <= 0 || experts <= 0 || top_k <= 0)
     return HB_ERR_BAD_ARG;
   if (n_entries == 0) return HB_OK;
   if (dtype == HB_DTYPE_F32)
-    return launch_grouped<float>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, active, experts, scores, act,
-                                 n_entries, inter, hidden, few_rows, stream);
+    return launch_grouped<float>(mode, x, hidden, sorted_entry, top_k, mode == 2 ? w_up : w_gate, w_up, offsets, active,
+                                 experts, scores, act, n_entries, inter, hidden, few_rows, stream);
   if (dtype == HB_DTYPE_BF16)
-    return launch_grouped<__nv_bfloat16>(true, x, hidden, sorted_entry, top_k, w_gate, w_up, offsets, active, experts, scores,
-                                         act, n_entries, inter, hidden, few_rows, stream);
+    return launch_grouped<__nv_bfloat16>(mode, x, hidden, sorted_entry, top_k, mode == 2 ? w_up : w_gate, w_up, offsets,
+                                         active, experts, scores, act, n_entries, inter, hidden, few_rows, stream);
   return HB_ERR_BAD_ARG;
 }
 
@@ -752,10 +806,10 @@ extern "C" int hb_moe_down(const void* act, int dtype, const void* w_down, const
     return HB_ERR_BAD_ARG;
   if (n_entries == 0) return HB_OK;
   if (dtype == HB_DTYPE_F32)
-    return launch_grouped<float>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, active, experts, nullptr, y,
+    return launch_grouped<float>(0, act, inter, nullptr, 1, w_down, nullptr, offsets, active, experts, nullptr, y,
                                  n_entries, hidden, inter, few_rows, stream);
   if (dtype == HB_DTYPE_BF16)
-    return launch_grouped<__nv_bfloat16>(false, act, inter, nullptr, 1, w_down, nullptr, offsets, active, experts, nullptr, y,
+    return launch_grouped<__nv_bfloat16>(0, act, inter, nullptr, 1, w_down, nullptr, offsets, active, experts, nullptr, y,
                                          n_entries, hidden, inter, few_rows, stream);
   return HB_ERR_BAD_ARG;
 }

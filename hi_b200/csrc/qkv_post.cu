@@ -130,21 +130,129 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
   }
 }
 
+// The general form: any head_dim, any number of rotating pairs, and an RMS norm of q and k that comes
+// BEFORE the rotation, over the first `norm_dim` dims of a head (the rest are padding and stay zero),
+// with a weight per dim (q_w / k_w [hd] float32, or null: no weight), shared by all heads:
+//   x <- x * rsqrt(mean_{d < norm_dim} x_d^2 + eps) * w;   pairs rotate by pos * inv_freq[j], and both
+//   cos and sin are multiplied by rot_mul (a scaling rule's magnitude factor).
+// norm_first == 0 keeps the other order of the kernel above (rotate, then the weightless norm over hd).
+// A block is one token; a warp takes a head at a time through a row of shared memory.
+template <typename T>
+__global__ void qkv_post_general_kernel(const T* __restrict__ qkv, const float* __restrict__ inv_freq, int rot_pairs,
+                                        int interleaved, int qk_norm, float qk_eps, int temp_on, float floor_scale,
+                                        float attn_scale, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                                        int norm_first, int norm_dim, float rot_mul,
+                                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                        const int* __restrict__ block_table, int table_stride, T* __restrict__ q_out,
+                                        T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size, int write_kv,
+                                        int nh, int nkv, int hd) {
+  extern __shared__ float smem_g[];            // [rot_pairs] cos, [rot_pairs] sin, [warps][hd] rows
+  float* cs = smem_g;
+  float* sn = cs + rot_pairs;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float* row = sn + rot_pairs + warp * hd;
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  for (int j = threadIdx.x; j < rot_pairs; j += blockDim.x) {
+    float s_, c_;
+    sincosf((float)pos * inv_freq[j], &s_, &c_);
+    cs[j] = c_ * rot_mul;
+    sn[j] = s_ * rot_mul;
+  }
+  __syncthreads();
+  const int heads_total = nh + 2 * nkv;
+  const int rot = 2 * rot_pairs;
+  for (int head = warp; head < heads_total; head += nwarps) {
+    const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);
+    if (kind != 0 && !write_kv) break;          // heads are ordered q, k, v
+    T* dst;
+    if (kind == 0) {
+      dst = q_out + ((size_t)t * nh + head) * hd;
+    } else {
+      const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
+      if (page < 0) continue;                   // the host reserves pages before the step
+      const int kvh = kind == 1 ? head - nh : head - nh - nkv;
+      dst = (kind == 1 ? k_pages : v_pages) + (((size_t)page * nkv + kvh) * page_size + (pos % page_size)) * hd;
+    }
+    const T* src = qkv + ((size_t)t * heads_total + head) * hd;
+    if (kind == 2) {
+      for (int d = lane; d < hd; d += 32) dst[d] = src[d];
+      continue;
+    }
+    const float* w = kind == 0 ? q_w : k_w;
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      const float x = hb::to_f32(src[d]);
+      row[d] = x;
+      if (d < norm_dim) ss += x * x;
+    }
+    ss = hb::warp_sum(ss);
+    float pre = 1.f, post = 1.f;
+    if (qk_norm) {
+      const float inv = rsqrtf(ss / (float)norm_dim + qk_eps);   // a rotation by rot_mul = 1 keeps the sum of squares
+      if (norm_first) pre = inv; else post = inv;
+    }
+    if (kind == 0 && temp_on) post *= logf(floorf(((float)pos + 1.f) / floor_scale) + 1.f) * attn_scale + 1.f;
+    __syncwarp();
+    if (norm_first && qk_norm) {
+      for (int d = lane; d < hd; d += 32) row[d] = row[d] * pre * (w ? w[d] : 1.f);
+      __syncwarp();
+    }
+    for (int d = lane; d < hd; d += 32) {
+      float y = row[d];
+      if (d < rot) {
+        if (interleaved) {
+          const int j = d >> 1;
+          y = (d & 1) ? row[d] * cs[j] + row[d - 1] * sn[j] : row[d] * cs[j] - row[d + 1] * sn[j];
+        } else {
+          y = d < rot_pairs ? row[d] * cs[d] - row[d + rot_pairs] * sn[d]
+                            : row[d] * cs[d - rot_pairs] + row[d - rot_pairs] * sn[d - rot_pairs];
+        }
+      }
+      dst[d] = hb::from_f32<T>(y * post);
+    }
+    __syncwarp();
+  }
+}
+
 }  // namespace
 
 extern "C" int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, int rot_pairs, int interleaved,
                            int qk_norm, float qk_eps, int temp_on, float floor_scale, float attn_scale,
+                           const float* q_norm_w, const float* k_norm_w, int norm_first, int norm_dim, float rot_mul,
                            const int* positions, const int* seq_of_token, const int* block_table,
                            int table_stride, void* q_out, void* k_pages, void* v_pages, int page_size,
                            int write_kv, int n_tokens, int nh, int nkv, int hd, cudaStream_t stream) {
   if (!qkv || !positions || !q_out || n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0) return HB_ERR_BAD_ARG;
   if (write_kv && (!k_pages || !v_pages || !block_table || !seq_of_token || page_size <= 0 || table_stride <= 0))
     return HB_ERR_BAD_ARG;
-  if (hd % 16 != 0 || hd > kMaxHeadDim) return HB_ERR_UNSUPPORTED;
   if (!inv_freq) rot_pairs = 0;
-  if (rot_pairs < 0 || 2 * rot_pairs > hd || rot_pairs % 8 != 0) return HB_ERR_UNSUPPORTED;  // whole lanes rotate
+  if (rot_pairs < 0 || 2 * rot_pairs > hd) return HB_ERR_UNSUPPORTED;
   if (temp_on && !(floor_scale > 0.f)) return HB_ERR_BAD_ARG;
+  if (norm_dim <= 0) norm_dim = hd;
+  if (norm_dim > hd || 2 * rot_pairs > norm_dim) return HB_ERR_BAD_ARG;
   if (n_tokens == 0) return HB_OK;
+  const bool fast = hd % 16 == 0 && hd <= kMaxHeadDim && rot_pairs % 8 == 0 /* whole lanes rotate */ && !norm_first &&
+                    !q_norm_w && !k_norm_w && norm_dim == hd && rot_mul == 1.f;
+  if (!fast) {
+    // a norm after a rotation that changes lengths would need the rotated squares; no model asks for it
+    if (qk_norm && !norm_first && (rot_mul != 1.f || q_norm_w || k_norm_w)) return HB_ERR_UNSUPPORTED;
+    const int heads_all = nh + 2 * nkv;
+    const int warps = heads_all < 8 ? heads_all : 8;
+    const size_t smem = (size_t)(2 * rot_pairs + warps * hd) * sizeof(float);
+    if (smem > 48 * 1024) return HB_ERR_UNSUPPORTED;
+#define HB_QKV_GENERAL(T)                                                                                          \
+    qkv_post_general_kernel<T><<<n_tokens, warps * 32, smem, stream>>>(                                             \
+        (const T*)qkv, inv_freq, rot_pairs, interleaved, qk_norm, qk_eps, temp_on, floor_scale, attn_scale, q_norm_w, \
+        k_norm_w, norm_first, norm_dim, rot_mul, positions, seq_of_token, block_table, table_stride, (T*)q_out,     \
+        (T*)k_pages, (T*)v_pages, page_size, write_kv, nh, nkv, hd)
+    if (dtype == HB_DTYPE_F32) HB_QKV_GENERAL(float);
+    else if (dtype == HB_DTYPE_BF16) HB_QKV_GENERAL(__nv_bfloat16);
+    else return HB_ERR_BAD_ARG;
+#undef HB_QKV_GENERAL
+    HB_LAUNCH_CHECK();
+    return HB_OK;
+  }
   const int heads_total = nh + 2 * nkv;
   int lanes_per_head = 1;
   while (lanes_per_head * 16 < hd) lanes_per_head *= 2;

@@ -18,22 +18,24 @@ P, I, F = c_void_p, c_int, c_float
 
 _SIGNATURES = {
     "hb_feed_tokens": [P, P, P, P, I, P],
-    "hb_embed_gather": [P, I, P, P, I, I, I, P],
-    "hb_add_rmsnorm": [P, P, I, P, P, P, I, P, I, P, I, P, P, I, I, F, P],
+    "hb_embed_gather": [P, I, P, P, I, I, I, F, P],
+    "hb_add_rmsnorm": [P, P, I, P, P, P, I, P, I, P, I, P, P, I, I, F, F, I, P],
     "hb_swiglu": [P, P, I, I, I, P],
+    "hb_relu2": [P, I, P, I, c_longlong, P],
+    "hb_softcap": [P, F, c_longlong, P],
     "hb_moe_combine": [P, P, P, P, I, P, I, I, I, P],
-    "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
-    "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
-    "hb_attention_merge": [P, P, P, I, I, I, I, P],
-    "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
-    "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P],
+    "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, I, I, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
+    "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
+    "hb_attention_merge": [P, P, P, I, I, I, I, I, P],
+    "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
+    "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
     "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P],
-    "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
-    "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, P, P, P],
-    "hb_router_topk": [P, I, P, I, I, I, I, I, I, P, P, P, P],
+    "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
+    "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
+    "hb_router_topk": [P, I, P, I, I, I, I, I, I, F, P, P, P, P],
     "hb_moe_plan": [P, I, I, P, P, P, P, P],
-    "hb_router_plan": [P, I, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P],
-    "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, P],
+    "hb_router_plan": [P, I, P, I, I, I, I, I, I, F, P, P, P, P, P, P, P, P, P],
+    "hb_moe_gate_up": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, P],
     "hb_moe_down": [P, I, P, P, P, I, P, I, I, I, I, P],
     "hb_gather_rows": [P, P, I, P, I, I, P],
     "hb_moe_gate_up_tc": [P, P, P, P, P, I, P, P, I, I, I, P, P],
@@ -52,6 +54,9 @@ _SIGNATURES = {
     "hb_delta_conv_update": [P, I, c_longlong, I, P, c_longlong, c_longlong, P, P, I, I, I, P],
     "hb_delta_recurrence": [P, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, I, I, P],
     "hb_delta_out_norm": [P, P, I, P, F, P, I, c_longlong, I, P],
+    "hb_mlstm_gates": [P, P, P, F, P, c_longlong, c_longlong, P, P, P, P, P, I, I, P],
+    "hb_mlstm_recurrence": [P, I, c_longlong, I, I, I, F, P, P, P, c_longlong, P, P, P, P, I, I, I, I, I, P],
+    "hb_mlstm_out_norm": [P, P, P, P, I, c_longlong, I, P, I, F, P, I, c_longlong, I, I, P],
 }
 
 _UNSUPPORTED = 1002
@@ -127,9 +132,10 @@ def feed_tokens(tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, samp
     _check(lib().hb_feed_tokens(_ptr(tokens), _ptr(dst), _ptr(src), _ptr(sampled), dst.numel(), _stream()), "feed_tokens")
 
 
-def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Rows of ``table`` [V, H] for int32 ``tokens`` [N] -> float32 residual stream [N, H] (into ``out``
-    if given)."""
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 scale: float = 1.0) -> torch.Tensor:
+    """Rows of ``table`` [V, H] for int32 ``tokens`` [N], times ``scale`` -> float32 residual stream [N, H]
+    (into ``out`` if given)."""
     _need(table, "table"); _need(tokens, "tokens", torch.int32)
     n, (vocab, hidden) = tokens.numel(), table.shape
     if out is None:
@@ -138,7 +144,7 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.
         _need(out, "out", torch.float32)
         if tuple(out.shape) != (n, hidden):
             raise KernelError(f"out has shape {tuple(out.shape)}, expected {(n, hidden)}")
-    _check(lib().hb_embed_gather(_ptr(table), _dt(table), _ptr(tokens), _ptr(out), n, hidden, vocab, _stream()),
+    _check(lib().hb_embed_gather(_ptr(table), _dt(table), _ptr(tokens), _ptr(out), n, hidden, vocab, float(scale), _stream()),
            "embed_gather")
     return out
 
@@ -146,8 +152,12 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
                 out_dtype: torch.dtype, row_map: Optional[torch.Tensor] = None, also_f32: bool = False,
                 routed: Optional[torch.Tensor] = None, slot_of_entry: Optional[torch.Tensor] = None,
-                top_k: int = 0, routed_weight: Optional[torch.Tensor] = None):
-    """``x += delta`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
+                top_k: int = 0, routed_weight: Optional[torch.Tensor] = None, x_scale: float = 1.0,
+                post: bool = False):
+    """``x = x_scale * x + delta`` (float32, in place) then ``rmsnorm(x) * weight`` in ``out_dtype``.
+
+    ``post``: the norm comes after the sum in the block, so the stream itself takes the normalised rows
+    (unrounded float32) instead of the sum; the returned ``y`` is the same rows in ``out_dtype``.
 
     ``routed`` (float32 [N*k, H], rows in expert-sorted order) with ``slot_of_entry`` adds each
     token's k routed-expert rows into the same sum: the experts' combine, fused into the norm;
@@ -172,6 +182,8 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
             raise KernelError(f"norm weight has {weight.numel()} elements for hidden size {hidden}")
     rows = rows_total
     if row_map is not None:
+        if post:
+            raise KernelError("a norm that writes the stream works on all rows (no row_map)")
         _need(row_map, "row_map", torch.int32)
         rows = row_map.numel()
     y = torch.empty((rows, hidden), dtype=out_dtype, device=x.device)
@@ -190,7 +202,7 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional
                                 _ptr(slot_of_entry), _ptr(routed_weight) if routed is not None else None, int(top_k),
                                 _ptr(weight),
                                 _dt(weight) if weight is not None else 0, _ptr(y), _dt(y), _ptr(y32), _ptr(row_map),
-                                rows, hidden, float(eps), _stream()), "add_rmsnorm")
+                                rows, hidden, float(eps), float(x_scale), 1 if post else 0, _stream()), "add_rmsnorm")
     if also_f32:
         return y, (y if y32 is None else y32)
     return y
@@ -205,6 +217,21 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _check(lib().hb_swiglu(_ptr(gate_up), _ptr(out), _dt(gate_up), n, two_i // 2, _stream()), "swiglu")
     return out
+
+
+def relu2(x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """max(x, 0)^2 in float32 math; the result in ``out_dtype`` (default: x's)."""
+    _need(x, "x")
+    out = torch.empty_like(x, dtype=out_dtype or x.dtype)
+    _check(lib().hb_relu2(_ptr(x), _dt(x), _ptr(out), _dt(out), x.numel(), _stream()), "relu2")
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), float32, in place."""
+    _need(x, "x", torch.float32)
+    _check(lib().hb_softcap(_ptr(x), float(cap), x.numel(), _stream()), "softcap")
+    return x
 
 
 # --------------------------------------------------------------------------- gated parallel block
@@ -405,6 +432,75 @@ def delta_out_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
     return out
 
 
+# --------------------------------------------------------------------------- mLSTM matrix memory
+def mlstm_state_floats(heads: int, dim: int, vdim: int) -> int:
+    """Floats of a request's state row: S column by column with n as one more column, then m per head."""
+    return heads * (vdim + 1) * dim + heads
+
+
+def mlstm_gates(z: torch.Tensor, bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor], cap: float,
+                state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, heads: int, dim: int, vdim: int):
+    """From the gates' pre-activations ``z`` float32 [N, 2 * heads] (input gates, then forget gates):
+    i = cap tanh((z_i + b_i) / cap), f = logsigmoid(cap tanh((z_f + b_f) / cap)), the running maximum
+    m' = max(f + m, i) token after token from the request's state (which takes the last m), and per
+    (token, head) ``keep`` = e^(f + m - m'), ``take`` = e^(i - m'), ``floor`` = e^(-m'), float32 [N, heads]."""
+    _need(z, "z", torch.float32); _need(state, "state", torch.float32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32); _need(slots, "slots", torch.int32)
+    n = z.shape[0]
+    if z.shape[1] != 2 * heads or state.dim() != 2 or state.shape[1] < mlstm_state_floats(heads, dim, vdim):
+        raise KernelError("gate pre-activations or the state row do not match the heads and sizes")
+    for b in (bias_i, bias_f):
+        if b is not None:
+            _need(b, "gate bias", torch.float32)
+            if b.numel() != heads:
+                raise KernelError("a gate bias has one number per head")
+    keep, take, floor = (torch.empty((n, heads), dtype=torch.float32, device=z.device) for _ in range(3))
+    _check(lib().hb_mlstm_gates(_ptr(z), _ptr(bias_i), _ptr(bias_f), float(cap), _ptr(state), state.stride(0),
+                                heads * (vdim + 1) * dim, _ptr(cu_seqlens), _ptr(slots), _ptr(keep), _ptr(take),
+                                _ptr(floor), slots.numel(), heads, _stream()), "mlstm_gates")
+    return keep, take, floor
+
+
+def mlstm_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_scale: float, keep: torch.Tensor,
+                     take: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor,
+                     heads: int, dim: int, vdim: int, rows_per_lane: int = 0):
+    """S <- keep S + take k v^T and n <- keep n + take k token after token, from and into the requests' state
+    rows; q, k [heads, dim] and v [heads, vdim] of a token are column runs of ``proj`` [N, ld] at the given
+    offsets, q times ``q_scale``. Returns S^T q float32 [N, heads, vdim] and n . q float32 [N, heads]."""
+    _need(proj, "proj"); _need(keep, "keep", torch.float32); _need(take, "take", torch.float32)
+    _need(state, "state", torch.float32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32); _need(slots, "slots", torch.int32)
+    n, ld = proj.shape
+    if max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim) > ld or tuple(keep.shape) != (n, heads):
+        raise KernelError("the projection's columns or the gates do not match the heads and sizes")
+    if state.dim() != 2 or state.shape[1] < mlstm_state_floats(heads, dim, vdim):
+        raise KernelError("the state row is too short for this memory")
+    o = torch.empty((n, heads, vdim), dtype=torch.float32, device=proj.device)
+    nq = torch.empty((n, heads), dtype=torch.float32, device=proj.device)
+    _check(lib().hb_mlstm_recurrence(_ptr(proj), _dt(proj), ld, q_off, k_off, v_off, float(q_scale), _ptr(keep),
+                                     _ptr(take), _ptr(state), state.stride(0), _ptr(cu_seqlens), _ptr(slots), _ptr(o),
+                                     _ptr(nq), slots.numel(), heads, dim, vdim, int(rows_per_lane), _stream()),
+           "mlstm_recurrence")
+    return o, nq
+
+
+def mlstm_out_norm(o: torch.Tensor, nq: torch.Tensor, floor: torch.Tensor, proj: torch.Tensor, g_off: int,
+                   weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """h = o / (max(|n . q|, floor) + 1e-6) per (token, head), h / sqrt(mean h^2 + eps) over the head's values,
+    times ``weight`` [heads * vdim], times the sigmoid of the gate (columns ``g_off`` .. of ``proj``);
+    [N, heads * vdim] in ``out_dtype``."""
+    _need(o, "o", torch.float32); _need(nq, "nq", torch.float32); _need(floor, "floor", torch.float32)
+    _need(proj, "proj"); _need(weight, "weight")
+    n, heads, vdim = o.shape
+    if weight.numel() != heads * vdim or g_off + heads * vdim > proj.shape[1] or proj.shape[0] != n:
+        raise KernelError("the norm weight or the gate columns do not match the heads and sizes")
+    out = torch.empty((n, heads * vdim), dtype=out_dtype, device=o.device)
+    _check(lib().hb_mlstm_out_norm(_ptr(o), _ptr(nq), _ptr(floor), _ptr(proj), _dt(proj), proj.shape[1], g_off,
+                                   _ptr(weight), _dt(weight), float(eps), _ptr(out), _dt(out), n, heads, vdim,
+                                   _stream()), "mlstm_out_norm")
+    return out
+
+
 def moe_combine(y: torch.Tensor, slot_of_entry: torch.Tensor, shared: Optional[torch.Tensor], n: int,
                 top_k: int, routed_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = shared[t] + sum_j w[t*k + j] * y[slot_of_entry[t*k + j]]  -> float32 [n, H] (w = 1 without
@@ -439,8 +535,15 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
              inv_freq: Optional[torch.Tensor], interleaved: bool, qk_norm: bool, qk_eps: float,
              temperature: Optional[Tuple[float, float]], seq_of_token: Optional[torch.Tensor],
              block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
-             v_pages: Optional[torch.Tensor], page_size: int, write_kv: bool) -> torch.Tensor:
+             v_pages: Optional[torch.Tensor], page_size: int, write_kv: bool,
+             q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
+             norm_first: bool = False, norm_dim: int = 0, rot_mul: float = 1.0) -> torch.Tensor:
     """Rotary or temperature, optional L2 norm, and the cache append; returns q [N, nh, hd].
+
+    By default the norm of q and k is weightless and comes after the rotation. ``norm_first``: it comes
+    before, over the first ``norm_dim`` dims of a head (0: all; dims past them are padding), times
+    ``q_norm_weight`` / ``k_norm_weight`` (float32 [hd], shared by the heads). ``rot_mul`` multiplies
+    cos and sin. Any even number of rotating dims is taken then (a general kernel runs these forms).
 
     ``qkv`` is [N, (nh + 2*nkv) * hd]; ``k_pages``/``v_pages`` are [pages, nkv, page_size, hd];
     ``block_table`` [S, width] int32 maps (sequence row, position // page_size) to a page.
@@ -449,9 +552,21 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
     n = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * hd:
         raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(nh + 2 * nkv) * hd}")
-    if hd % 16 != 0 or hd > 256:
-        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256)")
-    rot_pairs = _rot_pairs(inv_freq, hd)
+    general = norm_first or q_norm_weight is not None or k_norm_weight is not None or rot_mul != 1.0 or \
+        (norm_dim not in (0, hd)) or (inv_freq is not None and inv_freq.numel() % 8 != 0)
+    if hd % 8 != 0 or hd > 512 or (not general and (hd % 16 != 0 or hd > 256)):
+        raise KernelError(f"head_dim {hd} is not supported (multiples of 16 up to 256; the general form: of 8 up to 512)")
+    if general:
+        rot_pairs = 0 if inv_freq is None else inv_freq.numel()
+        if inv_freq is not None:
+            _need(inv_freq, "inv_freq", torch.float32)
+        for wt, nm in ((q_norm_weight, "q_norm_weight"), (k_norm_weight, "k_norm_weight")):
+            if wt is not None:
+                _need(wt, nm, torch.float32)
+                if wt.numel() != hd:
+                    raise KernelError(f"{nm} needs one weight per dim of a head ({hd})")
+    else:
+        rot_pairs = _rot_pairs(inv_freq, hd)
     stride = 0
     if write_kv:
         for t, nm in ((seq_of_token, "seq_of_token"), (block_table, "block_table")):
@@ -463,7 +578,8 @@ def qkv_post(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positions: torch.Ten
     q = torch.empty((n, nh, hd), dtype=qkv.dtype, device=qkv.device)
     fs, asc = temperature if temperature is not None else (1.0, 0.0)
     _check(lib().hb_qkv_post(_ptr(qkv), _dt(qkv), _ptr(inv_freq), rot_pairs, int(interleaved), int(qk_norm),
-                             float(qk_eps), int(temperature is not None), float(fs), float(asc), _ptr(positions),
+                             float(qk_eps), int(temperature is not None), float(fs), float(asc), _ptr(q_norm_weight),
+                             _ptr(k_norm_weight), int(norm_first), int(norm_dim), float(rot_mul), _ptr(positions),
                              _ptr(seq_of_token), _ptr(block_table), stride, _ptr(q), _ptr(k_pages), _ptr(v_pages),
                              page_size, int(write_kv), n, nh, nkv, hd, _stream()), "qkv_post")
     return q
@@ -486,8 +602,10 @@ DECODE_RESIDENT_BLOCKS = 148 * 3   # blocks of the decode kernel resident at a t
 
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                     seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int,
-                    scale: float, max_context: int = 0) -> torch.Tensor:
+                    scale: float, max_context: int = 0, sink: bool = False) -> torch.Tensor:
     """softmax(q k^T * scale) v over the keys each token may read; q [N, nh, hd] -> [N, nh, hd].
+    ``sink`` (here and in the other attention kernels): the softmax's denominator has one more term of
+    score 0, p_j = e^{s_j} / (1 + sum_j e^{s_j}); the term has no value.
 
     ``max_context`` (an upper bound of position + 1 over the tokens) lets long ranges be cut into
     splits of ``ATTENTION_SPLIT`` keys that run in parallel and are merged; a token's splits depend
@@ -516,8 +634,8 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         part_ml = torch.empty((n, nh, splits, 2), dtype=torch.float32, device=q.device)
     _check(lib().hb_paged_attention(_ptr(q), _dt(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                     block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv,
-                                    hd, page_size, int(chunk), int(window), float(scale), ATTENTION_SPLIT, splits,
-                                    _ptr(part_acc), _ptr(part_ml), _stream()),
+                                    hd, page_size, int(chunk), int(window), float(scale), int(sink), ATTENTION_SPLIT,
+                                    splits, _ptr(part_acc), _ptr(part_ml), _stream()),
            "paged_attention")
     return out
 
@@ -547,7 +665,7 @@ def decode_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int)
 
 def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                      seq_of_token: torch.Tensor, positions: torch.Tensor, chunk: int, window: int, scale: float,
-                     max_context: int) -> torch.Tensor:
+                     max_context: int, sink: bool = False) -> torch.Tensor:
     """Attention for a batch of single decoded tokens (every row of ``q`` is one request's
     token), bfloat16, split over runs of ``ATTENTION_SPLIT`` keys. Uses scratch memory for the
     partial results of the splits."""
@@ -574,20 +692,20 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     # tile loads by TMA where the range and the pages allow it (the kernel says if not)
     code = lib().hb_attention_decode_tma(_ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                                          block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv,
-                                         hd, page_size, int(chunk), int(window), float(scale), split_size, splits,
+                                         hd, page_size, int(chunk), int(window), float(scale), int(sink), split_size, splits,
                                          _ptr(part_acc), _ptr(part_ml), _ptr(_tc_status(q.device)), _stream())
     if code == _UNSUPPORTED:
         code = lib().hb_attention_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                                          _ptr(seq_of_token), _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size,
-                                         int(chunk), int(window), float(scale), split_size, splits, _ptr(part_acc),
-                                         _ptr(part_ml), _stream())
+                                         int(chunk), int(window), float(scale), int(sink), split_size, splits,
+                                         _ptr(part_acc), _ptr(part_ml), _stream())
         _check(code, "attention_decode")
     else:
         TC_USED[0] = True
         _check(code, "attention_decode_tma")
     if splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
-                                        _stream()), "attention_merge")
+                                        int(sink), _stream()), "attention_merge")
     return out
 
 
@@ -652,7 +770,7 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
     _check(code, "attention_decode_fused")
     if splits > 1 and not merge_inside:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
-                                        _stream()), "attention_merge")
+                                        0, _stream()), "attention_merge")
     return out
 
 
@@ -664,7 +782,7 @@ def prefill_attention_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: int
 def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
                       window: int, scale: float, skip_single: bool = False,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, sink: bool = False) -> torch.Tensor:
     """Attention for portions of prompts: request ``s`` owns rows ``cu_seqlens[s]..cu_seqlens[s+1]``
     of ``q`` [N, nh, hd], at consecutive positions; bfloat16, flash attention on tensor cores.
     ``skip_single`` leaves the rows of requests that bring one token unwritten (the caller runs
@@ -684,7 +802,8 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         out = torch.empty_like(q)
     _check(lib().hb_attention_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                                       _ptr(cu_seqlens), _ptr(positions), _ptr(out), n_seqs, int(max_new), nh, nkv, hd,
-                                      page_size, int(chunk), int(window), float(scale), int(skip_single), _stream()),
+                                      page_size, int(chunk), int(window), float(scale), int(skip_single), int(sink),
+                                      _stream()),
            "attention_prefill")
     return out
 
@@ -702,7 +821,7 @@ def prefill_attention_tc_supported(q_dtype: torch.dtype, nh: int, nkv: int, hd: 
 def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                          cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, max_new: int, chunk: int,
                          window: int, scale: float, skip_single: bool = False,
-                         out: Optional[torch.Tensor] = None, key_splits: int = 1) -> torch.Tensor:
+                         out: Optional[torch.Tensor] = None, key_splits: int = 1, sink: bool = False) -> torch.Tensor:
     """As :func:`prefill_attention`, on tcgen05 (S, P V and O in tensor memory, TMA page loads).
     ``key_splits`` > 1: that many blocks share the key tiles of every (query tile, head) and a
     merge kernel combines their rows (see :func:`prefill_key_splits`)."""
@@ -727,14 +846,15 @@ def prefill_attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     _check(lib().hb_attention_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                                          block_table.shape[1], _ptr(cu_seqlens), _ptr(positions), _ptr(out), n, n_pages,
                                          n_seqs, int(max_new), nh, nkv, hd, page_size, int(chunk), int(window),
-                                         float(scale), int(skip_single), key_splits, _ptr(part_acc) if part_acc is not None else None,
+                                         float(scale), int(skip_single), int(sink), key_splits,
+                                         _ptr(part_acc) if part_acc is not None else None,
                                          _ptr(part_ml) if part_ml is not None else None, _ptr(_tc_status(q.device)),
                                          _stream()),
            "attention_prefill_tc")
     TC_USED[0] = True
     if key_splits > 1:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, key_splits,
-                                        _stream()), "attention_merge")
+                                        int(sink), _stream()), "attention_merge")
     return out
 
 
@@ -778,7 +898,16 @@ def prefill_key_splits(blocks: int, key_tiles: int, sms: int) -> int:
 ROUTER_SOFTMAX, ROUTER_RENORMALIZE = 1, 2     # bits of a router's ``mode``
 
 
-def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool = False, mode: int = 0):
+def router_groups(count: int, keep: int) -> int:
+    """The bits of a router's ``mode`` that limit the choice to the ``keep`` best of ``count`` equal groups
+    of neighbouring experts (a group counts as the sum of its two largest sigmoid scores)."""
+    if not 0 < keep <= count <= 64:
+        raise KernelError(f"{keep} of {count} expert groups: up to 64 groups, at least one kept")
+    return (int(count) << 8) | (int(keep) << 16)
+
+
+def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool = False, mode: int = 0,
+                score_scale: float = 1.0):
     """Router logits (float32), the top-k expert ids (ties to the lower id) and their scores: the
     sigmoid of the chosen logit, or with ``ROUTER_SOFTMAX`` its softmax over all experts; with
     ``ROUTER_RENORMALIZE`` divided by the sum of the chosen scores."""
@@ -790,8 +919,8 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, want_logits: bool 
     ids = torch.empty((n, top_k), dtype=torch.int32, device=x.device)
     scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
     logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)   # the blocks' meeting place
-    _check(lib().hb_router_topk(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, int(mode), _ptr(logits),
-                                _ptr(ids), _ptr(scores), _stream()), "router_topk")
+    _check(lib().hb_router_topk(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, int(mode), float(score_scale),
+                                _ptr(logits), _ptr(ids), _ptr(scores), _stream()), "router_topk")
     return ids, scores, logits if want_logits else None
 
 
@@ -826,7 +955,7 @@ def _block_counter(dev) -> torch.Tensor:
     return c
 
 
-def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int, mode: int = 0):
+def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int, mode: int = 0, score_scale: float = 1.0):
     """:func:`router_topk` and :func:`moe_plan` in one call: with few tokens one kernel does both
     (the block that ends last groups the entries). Returns ids, scores and the plan."""
     _need(x, "x"); _need(w, "router weight")
@@ -838,8 +967,8 @@ def router_plan(x: torch.Tensor, w: torch.Tensor, top_k: int, mode: int = 0):
     scores = torch.empty((n, top_k), dtype=torch.float32, device=x.device)
     logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)   # the blocks' meeting place
     plan = _empty_plan(n * top_k, experts, x.device)
-    _check(lib().hb_router_plan(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, int(mode), _ptr(logits),
-                                _ptr(ids), _ptr(scores), _ptr(plan.offsets), _ptr(plan.sorted_entry),
+    _check(lib().hb_router_plan(_ptr(x), _dt(x), _ptr(w), _dt(w), n, hidden, experts, top_k, int(mode), float(score_scale),
+                                _ptr(logits), _ptr(ids), _ptr(scores), _ptr(plan.offsets), _ptr(plan.sorted_entry),
                                 _ptr(plan.slot_of_entry), _ptr(plan.active), _ptr(_block_counter(x.device)),
                                 _stream()), "router_plan")
     return ids, scores, plan
@@ -855,20 +984,26 @@ def moe_plan(ids: torch.Tensor, experts: int) -> MoePlan:
     return plan
 
 
-def moe_gate_up(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: torch.Tensor,
-                w_up: torch.Tensor, scores: torch.Tensor, few_rows: bool) -> torch.Tensor:
-    """act[slot] = silu(s * x Wg[e]^T) * (s * x Wu[e]^T), [N*k, I] in the engine dtype."""
-    _need(x, "x"); _need(w_gate, "w_gate", x.dtype); _need(w_up, "w_up", x.dtype)
+def moe_gate_up(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: Optional[torch.Tensor],
+                w_up: torch.Tensor, scores: torch.Tensor, few_rows: bool, activation: str = "swiglu") -> torch.Tensor:
+    """act[slot] = silu(s * x Wg[e]^T) * (s * x Wu[e]^T), [N*k, I] in the engine dtype; with
+    ``activation="relu2"`` (experts without a gate branch; ``w_gate`` None) max(s * x Wu[e]^T, 0)^2."""
+    _need(x, "x"); _need(w_up, "w_up", x.dtype)
     _need(scores, "scores", torch.float32)
+    if activation not in ("swiglu", "relu2") or (w_gate is None) != (activation == "relu2"):
+        raise KernelError("experts have a gate stack with swiglu and none with relu2")
     n, hidden = x.shape
-    experts, inter, h2 = w_gate.shape
-    if h2 != hidden or w_up.shape != w_gate.shape:
+    experts, inter, h2 = w_up.shape
+    if w_gate is not None:
+        _need(w_gate, "w_gate", x.dtype)
+    if h2 != hidden or (w_gate is not None and w_up.shape != w_gate.shape):
         raise KernelError("expert gate/up weights do not match the hidden size")
     n_entries = n * top_k
     act = torch.empty((n_entries, inter), dtype=x.dtype, device=x.device)
     _check(lib().hb_moe_gate_up(_ptr(x), _dt(x), _ptr(plan.sorted_entry), top_k, _ptr(w_gate), _ptr(w_up),
                                 _ptr(plan.offsets), _ptr(plan.active), experts, _ptr(scores), _ptr(act), n_entries,
-                                inter, hidden, int(few_rows), _stream()), "moe_gate_up")
+                                inter, hidden, int(few_rows), 1 if activation == "relu2" else 0, _stream()),
+           "moe_gate_up")
     return act
 
 
@@ -955,6 +1090,17 @@ def moe_tc_supported(x: torch.Tensor, w_gate: torch.Tensor) -> bool:
     multiples of 8 (TMA needs 16-byte row strides)."""
     return x.dtype == torch.bfloat16 and w_gate.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and \
         w_gate.shape[1] % 8 == 0
+
+
+def gather_rows(x: torch.Tensor, plan: MoePlan, top_k: int) -> torch.Tensor:
+    """The tokens' rows in expert order: xs[slot] = x[sorted_entry[slot] // top_k], bfloat16."""
+    _need(x, "x", torch.bfloat16)
+    n, hidden = x.shape
+    rows = n * top_k
+    xs = torch.empty((rows, hidden), dtype=x.dtype, device=x.device)
+    _check(lib().hb_gather_rows(_ptr(x), _ptr(plan.sorted_entry), top_k, _ptr(xs), rows, hidden, _stream()),
+           "gather_rows")
+    return xs
 
 
 def moe_gate_up_tc(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: torch.Tensor, w_up: torch.Tensor,

@@ -29,12 +29,13 @@ def _key_splits(ctx, nh: int, chunk: int, sliding: int, single: bool, device) ->
 
 
 def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, hd: int, chunk: int, sliding: int,
-                      scale: float):
+                      scale: float, sink: bool = False):
     """softmax(q k^T scale + mask) v for the step's tokens over the paged keys and values that are in
     the cache already, by the kernel that fits the step: single decoded tokens, portions of prompts
     (with single tokens of other requests beside them), or the general kernel for what those refuse
     (float32, other head sizes). ``q`` [N, nh, hd] -> [N, nh, hd]. Every mixer whose scores are dot
-    products over paged rows comes through here; ``k_pages`` and ``v_pages`` may be the same pool."""
+    products over paged rows comes through here; ``k_pages`` and ``v_pages`` may be the same pool.
+    ``sink``: the softmax's denominator has one more term of score 0 (it has no value)."""
     positions = ctx.positions
     # the decode kernel packs the query heads of one kv head into a 16-row tile; more heads on ONE shared kv
     # head go through it sixteen at a time
@@ -43,12 +44,13 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
 
     def decode(rows_q, seq, pos, longest):
         if per_call == nh:
-            return ops.decode_attention(rows_q, k_pages, v_pages, block_table, seq, pos, chunk, sliding, scale, longest)
+            return ops.decode_attention(rows_q, k_pages, v_pages, block_table, seq, pos, chunk, sliding, scale, longest,
+                                        sink=sink)
         out = torch.empty_like(rows_q)
         for first in range(0, nh, per_call):
             part = rows_q[:, first: first + per_call].contiguous()
             out[:, first: first + per_call] = ops.decode_attention(part, k_pages, v_pages, block_table, seq, pos, chunk,
-                                                                   sliding, scale, longest)
+                                                                   sliding, scale, longest, sink=sink)
         return out
 
     if ctx.max_new == 1 and decode_ok:
@@ -63,10 +65,10 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
         if tc:
             o = ops.prefill_attention_tc(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions,
                                          ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single,
-                                         key_splits=_key_splits(ctx, nh, chunk, sliding, single, q.device))
+                                         key_splits=_key_splits(ctx, nh, chunk, sliding, single, q.device), sink=sink)
         else:
             o = ops.prefill_attention(q, k_pages, v_pages, block_table, ctx.cu_seqlens, positions,
-                                      ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single)
+                                      ctx.n_seqs, ctx.max_new, chunk, sliding, scale, skip_single=single, sink=sink)
         if single:
             # single tokens beside portions: their long key ranges go through the split decode kernel
             rows = ctx.decode_rows
@@ -75,7 +77,7 @@ def attend_over_pages(q, k_pages, v_pages, block_table, ctx, nh: int, nkv: int, 
             o.index_copy_(0, rows, od)
         return o
     return ops.paged_attention(q, k_pages, v_pages, block_table, ctx.seq_of_token, positions,
-                               chunk, sliding, scale, ctx.max_context)
+                               chunk, sliding, scale, ctx.max_context, sink=sink)
 
 
 @register("mixer", "attention")
@@ -91,10 +93,18 @@ class AttentionMixer(Part):
       ``qk_norm``, ``qk_norm_eps``   weightless L2 norm of q and k after the rotation
       ``temperature``  None | (floor_scale, attn_scale): q *= 1 + attn_scale*ln(1 + floor((pos+1)/floor_scale))
       ``scale``        softmax scale; default head_dim ** -0.5 (models.rs:5963)
-      ``bias``         the random-weights writer makes ``<prefix>.{q,k,v,o}_proj.bias`` too
-    tensors: ``<prefix>.{q,k,v,o}_proj.weight``, and each projection's ``.bias`` where the
-    checkpoint has one (a bias is used iff its tensor exists: crates/hi-mlx/src/models.rs:1808,
-    1843-1845).
+      ``bias``         the random-weights writer makes the projections' biases too: True (all four) or a
+                       string of the projections that have one ("qkv")
+      ``value_dim``    size of a value head where it differs from ``head_dim`` (the query/key size). Keys,
+                       values and queries are then kept in rows of one padded size (the larger of the two,
+                       rounded up to 16): the projections get zero rows, the output projection zero columns
+      ``qk_norm_weighted``  the norm of q and k is an RMS norm BEFORE the rotation with a weight per dim,
+                       ``<prefix>.q.norm`` / ``<prefix>.k.norm`` [head_dim], shared by the heads
+      ``sink``         the softmax's denominator has one more term of score 0: exp(s_j) / (1 + sum exp(s_j))
+      ``names``        "proj" (default): ``<prefix>.{q,k,v,o}_proj.weight`` / ``.bias``;
+                       "short": ``<prefix>.{q,k,v,o}`` and ``<prefix>.{q,k,v,o}.b``
+    tensors: the four projections, and each projection's bias where the checkpoint has one (a bias is
+    used iff its tensor exists: crates/hi-mlx/src/models.rs:1808, 1843-1845).
     """
 
     graph_safe = True
@@ -107,15 +117,22 @@ class AttentionMixer(Part):
         self.nh, self.nkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
         if self.nh % self.nkv:
             raise ValueError(f"{prefix}: {self.nh} heads are not a multiple of {self.nkv} kv heads")
-        if self.hd % 16 or self.hd > 256:
-            raise ValueError(f"{prefix}: head_dim {self.hd} is not supported (multiples of 16 up to 256)")
+        self.dim, self.vdim = self.hd, int(p.get("value_dim") or self.hd)      # sizes as the checkpoint has them
+        self.norm_weighted = bool(p.get("qk_norm_weighted", False))
+        self.sink = bool(p.get("sink", False))
+        self.short_names = p.get("names", "proj") == "short"
+        if self.dim != self.vdim or self.dim % 16:
+            self.hd = -(-max(self.dim, self.vdim) // 16) * 16                  # rows of the cache and of q
+        if self.hd > (512 if self.hd != self.dim or self.norm_weighted else 256):
+            raise ValueError(f"{prefix}: head size {self.hd} is not supported")
         self.window = tuple(p["window"]) if p.get("window") else None
         self.position = build("position", p.get("position") or PartSpec("none"), env, prefix)
-        self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_norm = bool(p.get("qk_norm", False)) or self.norm_weighted
         self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
         self.temperature = tuple(p["temperature"]) if p.get("temperature") else None
-        self.scale = float(p.get("scale") or self.hd ** -0.5)
-        self.bias = bool(p.get("bias", False))
+        self.scale = float(p.get("scale") or self.dim ** -0.5)
+        self.bias = p.get("bias", False)
+        self.w_qnorm = self.w_knorm = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
@@ -124,32 +141,55 @@ class AttentionMixer(Part):
     def cache_spec(self):
         return CacheSpec(kv_heads=self.nkv, head_dim=self.hd, window=self.window)
 
+    def _name(self, proj: str, bias: bool = False) -> str:
+        if self.short_names:
+            return f"{self.prefix}.{proj}.b" if bias else f"{self.prefix}.{proj}"
+        return f"{self.prefix}.{proj}_proj.bias" if bias else f"{self.prefix}.{proj}_proj.weight"
+
     def tensor_specs(self):
-        h, nh, nkv, hd = self.hidden, self.nh, self.nkv, self.hd
-        init = "normal" if self.bias else "absent"     # "absent": the random-weights writer leaves them out
-        return [TensorSpec(f"{self.prefix}.q_proj.weight", (nh * hd, h)),
-                TensorSpec(f"{self.prefix}.k_proj.weight", (nkv * hd, h)),
-                TensorSpec(f"{self.prefix}.v_proj.weight", (nkv * hd, h)),
-                TensorSpec(f"{self.prefix}.o_proj.weight", (h, nh * hd)),
-                TensorSpec(f"{self.prefix}.q_proj.bias", (nh * hd,), init=init, optional=True),
-                TensorSpec(f"{self.prefix}.k_proj.bias", (nkv * hd,), init=init, optional=True),
-                TensorSpec(f"{self.prefix}.v_proj.bias", (nkv * hd,), init=init, optional=True),
-                TensorSpec(f"{self.prefix}.o_proj.bias", (h,), init=init, optional=True)]
+        h, nh, nkv = self.hidden, self.nh, self.nkv
+        have = "qkvo" if self.bias is True else (self.bias or "")
+        rows = {"q": nh * self.dim, "k": nkv * self.dim, "v": nkv * self.vdim, "o": h}
+        specs = [TensorSpec(self._name(n), (rows[n], h) if n != "o" else (h, nh * self.vdim)) for n in "qkvo"]
+        # "absent": the random-weights writer leaves them out
+        specs += [TensorSpec(self._name(n, bias=True), (rows[n],), init="normal" if n in have else "absent", optional=True)
+                  for n in "qkvo"]
+        if self.norm_weighted:
+            specs += [TensorSpec(f"{self.prefix}.{n}.norm", (self.dim,), init="ones") for n in "qk"]
+        return specs
+
+    def _pad_heads(self, t, heads: int, size: int):
+        """[heads * size, ...] -> [heads * hd, ...] with zero rows behind every head's own."""
+        if t is None or size == self.hd:
+            return t
+        out = torch.zeros((heads, self.hd, *t.shape[1:]), dtype=t.dtype, device=t.device)
+        out[:, :size] = t.view(heads, size, *t.shape[1:])
+        return out.view(heads * self.hd, *t.shape[1:])
 
     def load(self, fetch):
-        q, k, v = (fetch(f"{self.prefix}.{n}_proj.weight") for n in "qkv")
+        q, k, v = (fetch(self._name(n)) for n in "qkv")
         if not (q.dtype == k.dtype == v.dtype):
             q, k, v = q.float(), k.float(), v.float()
+        sizes = ((self.nh, self.dim), (self.nkv, self.dim), (self.nkv, self.vdim))
+        q, k, v = (self._pad_heads(t, *hs) for t, hs in zip((q, k, v), sizes))
         self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()     # one product for q, k and v
-        self.w_o = fetch(f"{self.prefix}.o_proj.weight").contiguous()
-        biases = [fetch(f"{self.prefix}.{n}_proj.bias") for n in "qkv"]
+        w_o = fetch(self._name("o"))
+        if self.vdim != self.hd:
+            w_o = self._pad_heads(w_o.t().contiguous(), self.nh, self.vdim).t()
+        self.w_o = w_o.contiguous()
+        biases = [fetch(self._name(n, bias=True)) for n in "qkv"]
         if any(b is not None for b in biases):          # a projection without one adds zeros
-            sizes = (self.nh * self.hd, self.nkv * self.hd, self.nkv * self.hd)
-            biases = [torch.zeros(n, dtype=self.w_qkv.dtype, device=self.w_qkv.device) if b is None else b
-                      for b, n in zip(biases, sizes)]
+            biases = [torch.zeros(hs[0] * self.hd, dtype=self.w_qkv.dtype, device=self.w_qkv.device) if b is None
+                      else self._pad_heads(b, *hs) for b, hs in zip(biases, sizes)]
             self.b_qkv = torch.cat([b.to(self.w_qkv.dtype) for b in biases]).contiguous()
-        b_o = fetch(f"{self.prefix}.o_proj.bias")
+        b_o = fetch(self._name("o", bias=True))
         self.b_o = None if b_o is None else b_o.to(self.w_o.dtype).contiguous()
+        if self.norm_weighted:
+            def weight(n):
+                w = torch.zeros(self.hd, dtype=torch.float32, device=self.w_qkv.device)
+                w[: self.dim] = fetch(f"{self.prefix}.{n}.norm").to(torch.float32)
+                return w
+            self.w_qnorm, self.w_knorm = weight("q"), weight("k")
 
     def forward(self, normed, ctx, cache):
         qkv = linear(normed, self.w_qkv, bias=self.b_qkv)
@@ -165,7 +205,9 @@ class AttentionMixer(Part):
         block_table = ctx.block_tables[cache.group]
         chunk = self.window[1] if self.window and self.window[0] == "chunk" else 0
         sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
-        if ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
+        rot_mul = float(getattr(self.position, "magnitude", 1.0))
+        plain = not (self.norm_weighted or self.sink or self.hd != self.dim or rot_mul != 1.0)
+        if plain and ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
             # a step of single decoded tokens: encoding, cache append, attention and the merge of its
             # splits in one launch, where the kernel takes the shapes
             o = ops.decode_attention_fused(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
@@ -175,7 +217,9 @@ class AttentionMixer(Part):
                 return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)
         q = ops.qkv_post(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
                          self.qk_norm_eps, self.temperature, ctx.seq_of_token, block_table, cache.k_pages,
-                         cache.v_pages, ctx.page_size, cache.writes)
+                         cache.v_pages, ctx.page_size, cache.writes, q_norm_weight=self.w_qnorm,
+                         k_norm_weight=self.w_knorm, norm_first=self.norm_weighted,
+                         norm_dim=0 if plain else self.dim, rot_mul=rot_mul)
         o = attend_over_pages(q, cache.k_pages, cache.v_pages, block_table, ctx, self.nh, self.nkv, self.hd, chunk,
-                              sliding, self.scale)
+                              sliding, self.scale, sink=self.sink)
         return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)

@@ -41,7 +41,8 @@ class Part:
 class RMSNorm(Part):
     """y = x * rsqrt(mean(x^2) + eps) * w, statistics in float32
     (crates/hi-mlx/src/models.rs:1977-1979; crates/hi-cuda/src/kernels.cu:61-77).
-    params: ``size``, ``eps``, ``name`` (tensor ``<prefix>.weight``)."""
+    params: ``size``, ``eps``, ``name`` (tensor ``<prefix>.weight``; with ``tensor`` = "bare" the tensor
+    is ``<prefix>`` itself)."""
 
     graph_safe = True
 
@@ -49,12 +50,13 @@ class RMSNorm(Part):
         super().__init__(params, prefix, env)
         self.size, self.eps = int(params["size"]), float(params["eps"])
         self.weight: Optional[torch.Tensor] = None
+        self.tensor_name = prefix if params.get("tensor") == "bare" else f"{prefix}.weight"
 
     def tensor_specs(self):
-        return [TensorSpec(f"{self.prefix}.weight", (self.size,), init="ones")]
+        return [TensorSpec(self.tensor_name, (self.size,), init="ones")]
 
     def load(self, fetch):
-        self.weight = fetch(f"{self.prefix}.weight").contiguous()
+        self.weight = fetch(self.tensor_name).contiguous()
 
     def forward(self, residual: torch.Tensor, delta, row_map: Optional[torch.Tensor] = None, also_f32: bool = False):
         """``delta``: None, a tensor, or a :class:`~hi_b200.parts.context.Pending`."""
@@ -182,6 +184,54 @@ class RotaryPosition(Part):
         return self._table, self.interleaved
 
 
+def yarn_inverse_frequencies(dims: int, base: float, scaling: Optional[dict]):
+    """(frequency of each of the dims / 2 pairs as float32, factor on cos and sin).
+
+    Pair i turns by base^(-2i/dims) per position. With ``scaling`` = {factor, original, fast, slow} the
+    pairs that turn fewer than ``slow`` times over ``original`` positions are slowed by ``factor``, those
+    that turn more than ``fast`` times stay, and a linear ramp over the pair index lies between:
+    with i(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(i(fast)), 0),
+    hi = min(ceil(i(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the
+    frequency is f_i / factor * ramp_i + f_i (1 - ramp_i); cos and sin grow by 0.1 ln(factor) + 1.
+    Worked out in float64, handed on in float32."""
+    half = dims // 2
+    f = np.array([base ** (-2.0 * i / dims) for i in range(half)], dtype=np.float64)
+    if not scaling:
+        return f.astype(np.float32), 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+    ramp = np.clip((np.arange(half, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).astype(np.float32), 0.1 * math.log(factor) + 1.0
+
+
+@register("position", "rope_yarn")
+class YarnRotaryPosition(Part):
+    """Rotary encoding of the first ``dims`` dims of a head (any even number; the rest pass through),
+    pairs (i, i + dims/2), with the ramped frequency scaling of :func:`yarn_inverse_frequencies` and its
+    factor on cos and sin (``magnitude``, which the encoding kernel takes as a multiplier).
+    params: ``head_dim``, ``dims``, ``base``, ``scaling`` ({factor, original, fast, slow} or None)."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.dims = int(params["dims"])
+        if self.dims % 2 or not 0 < self.dims <= int(params["head_dim"]):
+            raise ValueError(f"{prefix}: {self.dims} rotating dims must be even and at most head_dim")
+        self._table_host, self.magnitude = yarn_inverse_frequencies(self.dims, float(params["base"]), params.get("scaling"))
+        self._table: Optional[torch.Tensor] = None
+
+    def rotary_table(self):
+        if self._table is None:
+            self._table = torch.from_numpy(self._table_host).to(self.env.device)
+        return self._table, False
+
+
 @register("position", "none")
 class NoPosition(Part):
     """NoPE: q and k are used as projected."""
@@ -195,14 +245,15 @@ class NoPosition(Part):
 # --------------------------------------------------------------------------- embedding and head
 @register("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """x[t] = table[token[t]], no multiplier (crates/hi-mlx/src/models.rs:6206, 1915-1917).
-    params: ``vocab_size``, ``hidden_size``; tensor ``<prefix>.weight``."""
+    """x[t] = table[token[t]] * scale; no multiplier by default (crates/hi-mlx/src/models.rs:6206, 1915-1917).
+    params: ``vocab_size``, ``hidden_size``, ``scale`` (default 1); tensor ``<prefix>.weight``."""
 
     graph_safe = True
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.table: Optional[torch.Tensor] = None
+        self.scale = float(params.get("scale", 1.0))
 
     def tensor_specs(self):
         return [TensorSpec(f"{self.prefix}.weight", (int(self.params["vocab_size"]), int(self.params["hidden_size"])))]
@@ -211,14 +262,16 @@ class TokenEmbedding(Part):
         self.table = fetch(f"{self.prefix}.weight").contiguous()
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
-        return ops.embed_gather(self.table, tokens)
+        return ops.embed_gather(self.table, tokens, scale=self.scale)
 
 
 @register("head", "linear_head")
 class LinearHead(Part):
     """logits = z W^T in float32. The separate head is used when its tensor exists, else the
     embedding table (decided by presence, crates/hi-mlx/src/models.rs:6186-6193, 6211-6214).
-    params: ``vocab_size``, ``hidden_size``, ``tie`` (random weights: write no head tensor)."""
+    params: ``vocab_size``, ``hidden_size``, ``tie`` (random weights: write no head tensor),
+    ``softcap`` (None, or c: logits <- c tanh(logits / c)), ``tensor`` (the head tensor's whole name;
+    default ``<prefix>.weight``)."""
 
     graph_safe = True
 
@@ -226,20 +279,23 @@ class LinearHead(Part):
         super().__init__(params, prefix, env)
         self.weight: Optional[torch.Tensor] = None
         self.tied = False
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        self.tensor_name = params.get("tensor") or f"{prefix}.weight"
 
     def tensor_specs(self):
         # "absent": the random-weights writer leaves a tied head out of the folder
-        return [TensorSpec(f"{self.prefix}.weight", (int(self.params["vocab_size"]), int(self.params["hidden_size"])),
+        return [TensorSpec(self.tensor_name, (int(self.params["vocab_size"]), int(self.params["hidden_size"])),
                            init="absent" if self.params.get("tie", False) else "normal", optional=True)]
 
     def load(self, fetch):
-        w = fetch(f"{self.prefix}.weight")
+        w = fetch(self.tensor_name)
         self.tied = w is None
         self.weight = None if w is None else w.contiguous()
 
     def forward(self, normed_rows: torch.Tensor, embedding: TokenEmbedding) -> torch.Tensor:
         w = embedding.table if self.weight is None else self.weight
-        return linear(normed_rows, w, out_dtype=torch.float32)
+        logits = linear(normed_rows, w, out_dtype=torch.float32)
+        return logits if self.softcap is None else ops.softcap_(logits.contiguous(), self.softcap)
 
 
 # --------------------------------------------------------------------------- block arrangement
@@ -263,6 +319,60 @@ class PreNormBlock(Part):
             h = layer.norm_feed_forward.forward(residual, pending)
             pending = layer.feed_forward.forward(h, ctx)
         return residual, pending
+
+
+@register("arrangement", "postnorm")
+class PostNormBlock(Part):
+    """The norm comes after the sum: x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ff(x)).
+
+    The sub-layers read the stream itself (its rounding to the engine's dtype, which the norm kernel
+    writes beside the float32 stream). Each boundary is one kernel: the scaled stream, the sub-layer's
+    output and the routed experts' rows are summed in float32, normalised, and written back as the
+    stream. The first layer's mixer reads the embedding output, which no norm has touched: it is
+    rounded here. A layer without feed-forward has the first half only.
+
+    params: ``alpha`` (default 1)."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.alpha = float(params.get("alpha", 1.0))
+
+    def _boundary(self, norm, residual, delta):
+        """stream <- norm(alpha * stream + delta); returns the stream in the engine's dtype."""
+        if isinstance(delta, Pending):
+            if delta.routed is None:
+                delta = delta.dense
+            elif delta.top_k > 8:
+                delta = delta.materialize(residual.shape[0])
+        if isinstance(delta, Pending):
+            return ops.add_rmsnorm(residual, delta.dense, norm.weight, norm.eps, self.env.dtype, None, False,
+                                   delta.routed, delta.slot_of_entry, delta.top_k, delta.entry_weights,
+                                   x_scale=self.alpha, post=True)
+        return ops.add_rmsnorm(residual, delta, norm.weight, norm.eps, self.env.dtype, x_scale=self.alpha, post=True)
+
+    def forward(self, layer, residual, pending, ctx, cache_view):
+        if not isinstance(layer.norm_mixer, RMSNorm):
+            raise TypeError(f"{self.prefix}: the post-norm block works with rmsnorm norms")
+        if pending is not None:
+            raise TypeError(f"{self.prefix}: a post-norm block cannot follow a block that leaves a sum open")
+        # the stream in the engine's dtype, as the block before this one left it
+        owner, h = ctx.scratch.get("postnorm_stream", (None, None))
+        if owner is not residual:
+            h = residual if residual.dtype == self.env.dtype else residual.to(self.env.dtype)
+        y = layer.mixer.forward(h, ctx, cache_view)
+        h = self._boundary(layer.norm_mixer, residual, y)
+        if layer.feed_forward is not None:
+            if getattr(layer.feed_forward, "wants_f32_input", False):
+                y = layer.feed_forward.forward(h, ctx, normed_f32=residual)
+            else:
+                y = layer.feed_forward.forward(h, ctx)
+            h = self._boundary(layer.norm_feed_forward, residual, y)
+        ctx.scratch["postnorm_stream"] = (residual, h)
+        if ctx.tap is not None:
+            ctx.tap(f"{self.prefix}.stream_out", residual)
+        return residual, None
 
 
 _side_streams: Dict[torch.device, "torch.cuda.Stream"] = {}

@@ -65,10 +65,11 @@ class DenseMLP(Part):
     params: ``hidden_size``, ``intermediate_size``, ``activation``:
       "xielu"  z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2, with the
                two learned numbers (p, q) of ``<prefix>.act``; the coefficients are worked out once, in float32.
-    tensors: ``<prefix>.up`` [I, H], ``<prefix>.down`` [H, I], ``<prefix>.act`` [2]."""
+      "relu2"  max(z, 0)^2; no tensor of its own
+    tensors: ``<prefix>.up`` [I, H], ``<prefix>.down`` [H, I], ``<prefix>.act`` [2] (xielu)."""
 
     graph_safe = True
-    ACTIVATIONS = ("xielu",)
+    ACTIVATIONS = ("xielu", "relu2")
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -79,19 +80,22 @@ class DenseMLP(Part):
         self.w_up = self.w_down = self.coef = None
 
     def tensor_specs(self):
-        return [TensorSpec(f"{self.prefix}.up", (self.inter, self.hidden)),
-                TensorSpec(f"{self.prefix}.down", (self.hidden, self.inter)),
-                TensorSpec(f"{self.prefix}.act", (2,))]
+        specs = [TensorSpec(f"{self.prefix}.up", (self.inter, self.hidden)),
+                 TensorSpec(f"{self.prefix}.down", (self.hidden, self.inter))]
+        return specs + ([TensorSpec(f"{self.prefix}.act", (2,))] if self.activation == "xielu" else [])
 
     def load(self, fetch):
         self.w_up = fetch(f"{self.prefix}.up").contiguous()
         self.w_down = fetch(f"{self.prefix}.down").contiguous()
+        if self.activation != "xielu":
+            return
         pq = fetch(f"{self.prefix}.act").to(torch.float64)
         soft = torch.nn.functional.softplus(pq)
         self.coef = torch.stack([soft[0], 0.5 + soft[1]]).to(torch.float32).contiguous()
 
     def forward(self, normed, ctx):
-        return linear(ops.xielu(linear(normed, self.w_up), self.coef), self.w_down)
+        z = linear(normed, self.w_up)
+        return linear(ops.relu2(z) if self.activation == "relu2" else ops.xielu(z, self.coef), self.w_down)
 
 
 @register("feed_forward", "routed_experts")
@@ -108,6 +112,15 @@ class SigmoidRoutedExperts(Part):
       ``renormalize``  the chosen scores are divided by their sum (default False)
       ``scale``        "input" (default: the score multiplies what the expert reads) | "output"
                        (it multiplies what the expert returns, in the sum the next norm takes)
+      ``activation``   "swiglu" (default: gate and up stacks) | "relu2" (W_down max(W_up x, 0)^2: no gate stack;
+                       the score then has to scale the output)
+      ``groups``       None | (count, keep): the experts lie in ``count`` equal groups of neighbours, a group
+                       counts as the sum of its two largest scores, and only experts of the ``keep`` best
+                       groups can be chosen
+      ``score_scale``  a constant factor on every chosen score (default 1)
+      ``names``        "stacked" (default, the tensors below) | "per_expert": ``<prefix>.router`` [E, H] and for
+                       every expert i ``<prefix>.e<i>.up`` [I, H], ``<prefix>.e<i>.down`` [H, I] (and ``.gate``
+                       with swiglu), stacked at load
     tensors: ``<prefix>.router.weight`` [E, H]; ``<prefix>.experts.{gate,up}_proj.weight`` [E, I, H];
     ``<prefix>.experts.down_proj.weight`` [E, H, I]; ``<prefix>.shared_expert.{gate,up,down}_proj.weight``.
     """
@@ -133,15 +146,35 @@ class SigmoidRoutedExperts(Part):
         self.router_mode = (ops.ROUTER_SOFTMAX if score == "softmax" else 0) | \
             (ops.ROUTER_RENORMALIZE if params.get("renormalize", False) else 0)
         self.scale_output = scale == "output"
+        self.activation = params.get("activation", "swiglu")
+        if self.activation not in ("swiglu", "relu2") or (self.activation == "relu2" and not self.scale_output):
+            raise ValueError(f"{prefix}: activation {self.activation!r} is not known (swiglu | relu2), or relu2 "
+                             f"without scale 'output' (a score on the input would be squared)")
+        self.groups = tuple(int(g) for g in params["groups"]) if params.get("groups") else None
+        if self.groups:
+            count, keep = self.groups
+            if score != "sigmoid" or self.experts % count or not 0 < keep <= count or self.top_k > keep * (self.experts // count):
+                raise ValueError(f"{prefix}: {self.experts} sigmoid-scored experts do not form {count} equal groups of "
+                                 f"which {keep} hold {self.top_k} choices")
+            self.router_mode |= ops.router_groups(count, keep)
+        self.score_scale = float(params.get("score_scale", 1.0))
+        self.per_expert_names = params.get("names", "stacked") == "per_expert"
         self._ones: Optional[torch.Tensor] = None
         self.w_router = self.w_gate = self.w_up = self.w_down = None
         self._side_stream = None
 
     def tensor_specs(self):
         e, i, h, p = self.experts, self.inter, self.hidden, self.prefix
-        specs = [TensorSpec(f"{p}.router.weight", (e, h)),
-                 TensorSpec(f"{p}.experts.gate_proj.weight", (e, i, h)),
-                 TensorSpec(f"{p}.experts.up_proj.weight", (e, i, h)),
+        gated = self.activation == "swiglu"
+        if self.per_expert_names:
+            specs = [TensorSpec(f"{p}.router", (e, h))]
+            for j in range(e):
+                specs += ([TensorSpec(f"{p}.e{j}.gate", (i, h))] if gated else []) + \
+                    [TensorSpec(f"{p}.e{j}.up", (i, h)), TensorSpec(f"{p}.e{j}.down", (h, i))]
+        else:
+            specs = [TensorSpec(f"{p}.router.weight", (e, h))] + \
+                ([TensorSpec(f"{p}.experts.gate_proj.weight", (e, i, h))] if gated else []) + \
+                [TensorSpec(f"{p}.experts.up_proj.weight", (e, i, h)),
                  TensorSpec(f"{p}.experts.down_proj.weight", (e, h, i))]
         return specs + (self.shared.tensor_specs() if self.shared else [])
 
@@ -156,10 +189,17 @@ class SigmoidRoutedExperts(Part):
                     f"{self.env.dtype} path cannot take it (run with --dtype float32)")
             return t.contiguous()
 
-        self.w_router = expert_tensor(f"{p}.router.weight")
-        self.w_gate = expert_tensor(f"{p}.experts.gate_proj.weight")
-        self.w_up = expert_tensor(f"{p}.experts.up_proj.weight")
-        self.w_down = expert_tensor(f"{p}.experts.down_proj.weight")
+        gated = self.activation == "swiglu"
+        if self.per_expert_names:
+            stack = lambda part: torch.stack([expert_tensor(f"{p}.e{j}.{part}") for j in range(self.experts)]).contiguous()
+            self.w_router = expert_tensor(f"{p}.router")
+            self.w_gate = stack("gate") if gated else None
+            self.w_up, self.w_down = stack("up"), stack("down")
+        else:
+            self.w_router = expert_tensor(f"{p}.router.weight")
+            self.w_gate = expert_tensor(f"{p}.experts.gate_proj.weight") if gated else None
+            self.w_up = expert_tensor(f"{p}.experts.up_proj.weight")
+            self.w_down = expert_tensor(f"{p}.experts.down_proj.weight")
         if self.shared:
             self.shared.load(fetch)
 
@@ -186,7 +226,7 @@ class SigmoidRoutedExperts(Part):
         router_in = normed if normed_f32 is None else normed_f32
         forced = ctx.forced.get(f"{self.prefix}.router_ids") if ctx.forced else None
         if forced is None:
-            ids, scores, plan = ops.router_plan(router_in, self.w_router, self.top_k, self.router_mode)
+            ids, scores, plan = ops.router_plan(router_in, self.w_router, self.top_k, self.router_mode, self.score_scale)
         else:
             # debug: another run's expert choices, scored with this run's own logits (two runs in
             # different precisions can then be compared token by token)
@@ -197,7 +237,7 @@ class SigmoidRoutedExperts(Part):
                 torch.exp(chosen - torch.logsumexp(logits, dim=1, keepdim=True))
             if self.router_mode & ops.ROUTER_RENORMALIZE:
                 scores = scores / scores.sum(dim=1, keepdim=True)
-            scores = scores.contiguous()
+            scores = (scores * self.score_scale).contiguous()
             plan = ops.moe_plan(ids, self.experts)
         if ctx.tap is not None:
             ctx.tap(f"{self.prefix}.router_ids", ids)
@@ -207,14 +247,19 @@ class SigmoidRoutedExperts(Part):
             if self._ones is None or self._ones.numel() < scores.numel():
                 self._ones = torch.ones(max(scores.numel(), 65536), dtype=torch.float32, device=scores.device)
             entry_weights, scores = scores.view(-1), self._ones[: scores.numel()].view_as(scores)
-        tc = ops.moe_tc_supported(normed, self.w_gate)
+        tc = ops.moe_tc_supported(normed, self.w_up)
         few = n * self.top_k <= (self.FEW_ROWS if tc else 128)
-        if not few and tc:
+        if not few and tc and self.activation == "relu2":
+            # the up stack alone is a plain grouped product: the kernel of the down projection takes it
+            # (float32 out), the squared relu rounds it to the engine's dtype
+            up = ops.moe_down_tc(ops.gather_rows(normed, plan, self.top_k), self.w_up, plan)
+            y = ops.moe_down_tc(ops.relu2(up, normed.dtype), self.w_down, plan)
+        elif not few and tc:
             # many rows per expert: the grouped products run on tcgen05
             act = ops.moe_gate_up_tc(normed, plan, self.top_k, self.w_gate, self.w_up, scores)
             y = ops.moe_down_tc(act, self.w_down, plan)
         else:
-            act = ops.moe_gate_up(normed, plan, self.top_k, self.w_gate, self.w_up, scores, few)
+            act = ops.moe_gate_up(normed, plan, self.top_k, self.w_gate, self.w_up, scores, few, self.activation)
             y = ops.moe_down(act, self.w_down, plan, few)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)

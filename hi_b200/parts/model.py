@@ -10,6 +10,7 @@ from . import basic as _basic          # noqa: F401
 from . import delta_rule as _delta     # noqa: F401
 from . import feed_forward as _ffn     # noqa: F401
 from . import latent_attention as _latent  # noqa: F401
+from . import mlstm as _mlstm          # noqa: F401
 from .context import CacheView, StepContext
 from .registry import BuildEnv, build
 from .spec import CacheSpec, ModelSpec, PartSpec, TensorSpec
