@@ -159,29 +159,44 @@ def dense_ff(h, w, p):
     return relu_squared(h @ w[p + ".up"].T) @ w[p + ".down"].T
 
 
-def route(h, w, p, router: dict):
+def route(h, w, p, router: dict, forced=None, record=None):
     """(expert ids [T, top], weights [T, top]): scores are sigmoids of the router's logits; the experts lie
-    in ``groups.count`` equal groups of neighbours, a group counts as the sum of its two best scores, only
+    in ``groups.count`` equal groups of neighbours, a group counts as the sum of its two largest scores, only
     the ``groups.keep`` best groups stay open, the ``top`` best experts of those are taken, and each
-    weighs its score times ``scale``."""
+    weighs its score times ``scale``.
+
+    ``forced`` [T, top]: choices to take instead of the own ones (their weights are still the own scores).
+    ``record(ids, gap)`` gets the own choices and how clear they were: the smaller of the distance between the
+    last open and the first shut group's score and that between the last taken and the first left-out score."""
     s = torch.sigmoid(h @ w[p + ".router"].T)                                        # [T, E]
     t, e = s.shape
+    top = int(router["top"])
     groups = router.get("groups")
     allowed = torch.ones_like(s, dtype=torch.bool)
+    gap = torch.full((t,), float("inf"), dtype=s.dtype)
     if groups:
         count, keep = int(groups["count"]), int(groups["keep"])
         per = e // count
         best_two = s.view(t, count, per).topk(min(2, per), dim=2).values.sum(dim=2)  # [T, count]
-        open_groups = best_two.topk(keep, dim=1).indices
+        ranked = best_two.sort(dim=1, descending=True)
+        if keep < count:
+            gap = ranked.values[:, keep - 1] - ranked.values[:, keep]
         allowed = torch.zeros(t, count, dtype=torch.bool)
-        allowed.scatter_(1, open_groups, True)
+        allowed.scatter_(1, ranked.indices[:, :keep], True)
         allowed = allowed[:, :, None].expand(t, count, per).reshape(t, e)
-    chosen = s.masked_fill(~allowed, -1.0).topk(int(router["top"]), dim=1).indices
+    ranked = s.masked_fill(~allowed, -1.0).sort(dim=1, descending=True)
+    chosen = ranked.indices[:, :top]
+    if top < int(allowed[0].sum()):
+        gap = torch.minimum(gap, ranked.values[:, top - 1] - ranked.values[:, top])
+    if record is not None:
+        record(chosen, gap)
+    if forced is not None:
+        chosen = forced.long()
     return chosen, torch.gather(s, 1, chosen) * float(router.get("scale", 1.0))
 
 
-def moe_ff(h, w, p, mlp: dict):
-    ids, weights = route(h, w, p, mlp["router"])
+def moe_ff(h, w, p, mlp: dict, forced=None, record=None):
+    ids, weights = route(h, w, p, mlp["router"], forced, record)
     out = torch.zeros(h.shape[0], w[p + ".e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e, g in zip(ids[t].tolist(), weights[t]):
@@ -189,15 +204,16 @@ def moe_ff(h, w, p, mlp: dict):
     return out
 
 
-def feed_forward(h, w, p, mlp: dict):
-    return dense_ff(h, w, p) if mlp["kind"] == "dense" else moe_ff(h, w, p, mlp)
+def feed_forward(h, w, p, mlp: dict, forced=None, record=None):
+    return dense_ff(h, w, p) if mlp["kind"] == "dense" else moe_ff(h, w, p, mlp, forced, record)
 
 
 # --------------------------------------------------------------------------- the model
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], first_pos: int = 0, carried=None,
-            dtype=torch.float64, layers_out: Optional[list] = None):
+            dtype=torch.float64, layers_out: Optional[list] = None, forced_routing=None, record=None):
     """Logits [T, vocab] of ``tokens`` at positions first_pos .., and what the next portion needs
-    (``carried``: per layer the attention's keys/values/positions or the mLSTM's state)."""
+    (``carried``: per layer the attention's keys/values/positions or the mLSTM's state).
+    ``forced_routing`` {"l<i>.mlp": ids [T, top]} and ``record(name, ids, gap)``: see :func:`route`."""
     w = {k: v.to(dtype) if v.is_floating_point() else v for k, v in w.items()}
     eps, alpha = float(cfg["norm"]["eps"]), float(cfg.get("postln_alpha", 1.0))
     positions = torch.arange(first_pos, first_pos + len(tokens))
@@ -213,7 +229,10 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], first_pos:
             raise ValueError(layer["type"])
         x = rms(alpha * x + y, eps) * w[p + ".norm1"]
         if layer.get("mlp"):
-            x = rms(alpha * x + feed_forward(x, w, p + ".mlp", layer["mlp"]), eps) * w[p + ".norm2"]
+            name = p + ".mlp"
+            y = feed_forward(x, w, name, layer["mlp"], (forced_routing or {}).get(name),
+                             None if record is None else (lambda ids, gap, name=name: record(name, ids, gap)))
+            x = rms(alpha * x + y, eps) * w[p + ".norm2"]
         if layers_out is not None:
             layers_out.append(x.clone())
     z = (rms(x, eps) * w["final.norm"]) @ w["head"].T

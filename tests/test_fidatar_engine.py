@@ -1,0 +1,304 @@
+"""Fidatar in the engine against the plain implementation: the attention mixer alone, whole prompts, decoding
+through the cache and the state, portions down to two tokens, mixed batches with pages and slots used again,
+keys far away and at the chunks' edges under a peaked softmax, the first tokens, long decoding, five
+configurations of other sizes, generation through the entry point, the trace replay and the command line."""
+import numpy as np
+import pytest
+import torch
+
+import harness as h
+import plain_fidatar as plain
+from fidatar_configs import FD_A, FD_B, FD_C, FD_D, FD_E, PlainFidatar, make_weights, peaked, write_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+# A position's error is the largest difference of its logits over the largest logit. The float32 runs are the sharp
+# ones: rounding gives about 3e-5 there, while a lost, doubled or shifted key, a wrong window, a lost state or another
+# expert moves the logits by a thousand times that; up to 6 % of a comparison's positions may exceed the tolerance
+# (each head's output is normalised after sums that can nearly cancel), none 8 times.
+# In bfloat16 these small models magnify rounding too much for a bound per position: where a memory holds one token
+# whose key is nearly orthogonal to the query, the read-out is a small vector that the head's norm blows up to length
+# one, with the sign of a dot product that the rounding of q and k flips, and what follows inherits the difference.
+# There the MEDIAN error of a comparison's positions is held to the tolerance (a fault in a kernel that only
+# bfloat16 takes moves most positions by far more); each such kernel alone is compared sharply in test_fidatar_kernels.
+TOL = {"float32": 6e-5, "bfloat16": 6e-2}
+CONFIGS = {"A": FD_A, "B": FD_B, "C": FD_C, "D": FD_D, "E": FD_E}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    base = tmp_path_factory.mktemp("fidatar")
+    out = {}
+    for name, cfg in CONFIGS.items():
+        d = str(base / name)
+        out[name] = (cfg, d, write_model(d, cfg, seed=40 + ord(name)))
+    return out
+
+
+def tokens(cfg, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, cfg["vocab"], (n,), generator=g).tolist()
+
+
+def engine(mdir, dtype, **kw):
+    from hi_b200.engine.core import Engine
+
+    kw.setdefault("kv_page_size", 16)
+    kw.setdefault("kv_cache_tokens", 2048)
+    kw.setdefault("max_active_requests", 4)
+    return Engine.from_dir(mdir, dtype=dtype, **kw)
+
+
+def compare(cfg, weights, requests, got, tol, what, forced=None):
+    """Every wanted row against the plain model; names the first wrong token.
+
+    ``forced``: the engine's own expert choices in a bfloat16 run (reduced precision may pick the other of two
+    nearly equal scores; the logits are then compared given that choice)."""
+    over, errs = [], []
+    sharp = tol < 1e-3
+    for rid, toks in requests.items():
+        ref, _ = plain.forward(cfg, weights, toks, forced_routing=(forced or {}).get(rid))
+        scale = float(ref.abs().max())
+        rows = got.get(rid, {})
+        assert rows, f"{what}: no logits came back for request {rid!r}"
+        for p in sorted(rows):
+            err = float(np.abs(rows[p].astype(np.float64) - ref[p].numpy()).max()) / scale
+            assert np.isfinite(err), f"{what}: request {rid!r}, position {p}: not finite"
+            assert not sharp or err <= 8 * tol, (
+                f"{what}: request {rid!r} first differs at position {p} of {len(toks)}: rel err {err:.3e} > {8 * tol:.1e}")
+            errs.append(err)
+            if err > tol:
+                over.append((rid, p, err))
+    if sharp:
+        assert len(over) <= max(1, 0.06 * len(errs)), f"{what}: {len(over)} of {len(errs)} positions over {tol:.1e}; the first: {over[:3]}"
+    else:
+        assert float(np.median(errs)) <= tol, f"{what}: median error {float(np.median(errs)):.3e} of {len(errs)} positions > {tol:.1e}"
+
+
+# --------------------------------------------------------------------------- the attention mixer alone
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 2e-5), (torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("layer", [FD_A["layers"][0], FD_A["layers"][2], FD_A["layers"][4], FD_B["layers"][0], FD_B["layers"][2],
+                                   FD_D["layers"][0], FD_E["layers"][0], FD_E["layers"][2]])
+def test_attention_mixer_alone(dt, tol, layer):
+    """Two requests in three steps (a portion each, a portion beside a single token, single tokens) on
+    scattered pages; value heads narrower and wider than key heads; chunks that cut the pages anywhere."""
+    from hi_b200.parts.context import CacheView
+    from hi_b200.parts.fidatar import build_fidatar_spec
+    from hi_b200.config.fidatar import FidatarConfig
+    from hi_b200.parts.registry import build
+    from test_vinurax_engine import _ctx, _env
+
+    width, page, eps = 48, 8, 1e-5
+    m = layer["mixer"]
+    cfg = {"architecture": "Fidatar", "vocab": 8, "width": width, "norm": {"eps": eps}, "layers": [dict(layer, mlp=None)]}
+    w = make_weights(cfg, m["dim"] + m["heads"])
+    spec = build_fidatar_spec(FidatarConfig.from_json(cfg)).layers[0].mixer
+    part = build("mixer", spec, _env(dt, width), "l0.mix")
+    part.load(lambda name: w[name].to(DEV).to(dt) if name in w else None)
+    cs = part.cache_spec()
+    kp, vp = (torch.zeros((12, cs.kv_heads, page, cs.head_dim), dtype=dt, device=DEV) for _ in range(2))
+    view = CacheView(group=0, k_pages=kp, v_pages=vp, writes=True)
+    table = torch.tensor([[7, 2, 9, 4, 6], [1, 11, 0, 5, 3]], dtype=torch.int32)
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.randn(n, width, generator=g).to(dt).float() for n in (33, 29)]
+    cuts = [([13, 17], [0, 0]), ([18, 1], [13, 17]), ([1, 1], [31, 18]), ([1, 10], [32, 19])]
+    got = [[], []]
+    for lens, starts in cuts:
+        x = torch.cat([xs[i][s: s + n] for i, (n, s) in enumerate(zip(lens, starts))])
+        out = part.forward(x.to(DEV).to(dt), _ctx(lens, starts, page, table, [0, 1]), view)
+        a = 0
+        for i, n in enumerate(lens):
+            got[i].append(out[a: a + n].float().cpu())
+            a += n
+    wd = {k: v.double() for k, v in w.items()}
+    for i in range(2):
+        want, _ = plain.attention_mixer(xs[i].double(), torch.arange(xs[i].shape[0]), None, wd, "l0.mix", m, eps)
+        have = torch.cat(got[i]).double()
+        err = float((have - want).abs().max() / want.abs().max())
+        assert have.shape == want.shape and err <= tol, f"request {i}: rel err {err:.3e}"
+
+
+# --------------------------------------------------------------------------- the model in the engine
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_four_ways_of_cutting(name, dtype, models):
+    cfg, mdir, weights = models[name]
+    requests = {"p": tokens(cfg, 150, 1), "q": tokens(cfg, 37, 2), "r": tokens(cfg, 1, 3), "s": tokens(cfg, 2, 4),
+                "t": tokens(cfg, 64, 5), "u": tokens(cfg, 97, 6)}
+    eng = engine(mdir, dtype, kv_cache_tokens=352, debug_poison=True)
+    prompt = {r: min(len(t), max(2, len(t) - 24)) for r, t in requests.items()}      # the rest is decoded token by token
+    for what, steps in (("whole", h.trace_whole(requests)), ("decode", h.trace_tail_decode(requests, tail=20)),
+                        ("portions", h.trace_portions(requests)),
+                        ("mixed", h.trace_mixed(requests, max_tokens=352, page=16, seed=7, max_live=4, prefill_len=prompt))):
+        got, forced = h.replay_in_process(eng, steps, record_routing=(dtype == "bfloat16"))
+        compare(cfg, weights, requests, got, TOL[dtype], f"{name} {dtype} {what}", forced)
+    assert len(eng.manager.requests) == 0
+
+
+@pytest.mark.parametrize("name", ["A", "E"])
+def test_mixed_batches_use_pages_and_slots_again(name, models):
+    """More requests than slots and than the pool holds at once, in two orders: every request's logits equal
+    the plain model's whatever ran beside it and whichever pages and slot it got."""
+    cfg, mdir, weights = models[name]
+    requests = {i: tokens(cfg, n, 30 + i) for i, n in enumerate((70, 33, 48, 5, 90, 17, 64, 31, 2, 55))}
+    for seed, live in ((1, 4), (2, 2)):
+        eng = engine(mdir, "float32", kv_cache_tokens=272, max_active_requests=live, debug_poison=True)
+        steps = h.trace_mixed(requests, max_tokens=272, page=16, seed=seed, max_live=live)
+        got, _ = h.replay_in_process(eng, steps)
+        compare(cfg, weights, requests, got, TOL["float32"], f"{name} mixed seed {seed}")
+        assert eng.manager.snapshot()["groups"][0]["allocations"] > 272 // 16      # pages were handed out again
+
+
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_far_keys_and_chunk_edges_under_a_peaked_softmax(name, models, tmp_path):
+    """Attention scales times 8: nearly all weight on one key or on the sink, so a key that is one position
+    inside or outside a chunk, lost, doubled or shifted shows. A prompt over many pages and chunks whole, in
+    portions whose edges fall inside pages and chunks, and decoded at the end; every position is compared."""
+    cfg = peaked(CONFIGS[name], 8.0)
+    mdir = str(tmp_path / "peaked")
+    weights = write_model(mdir, cfg, seed=77)
+    requests = {"long": tokens(cfg, 460, 8), "short": tokens(cfg, 90, 9)}
+    eng = engine(mdir, "float32", kv_cache_tokens=1024)
+    for what, steps in (("whole", h.trace_whole(requests)), ("decode", h.trace_tail_decode(requests, tail=60)),
+                        ("portions", h.trace_portions(requests, sizes=(100, 3, 61, 2, 129, 17, 2, 90, 5))),
+                        ("mixed", h.trace_mixed(requests, max_tokens=1024, page=16, seed=3, max_live=2))):
+        got, _ = h.replay_in_process(eng, steps)
+        compare(cfg, weights, requests, got, 2e-4, f"{name} peaked {what}")
+
+
+def test_a_planted_key_at_a_chunks_edge(tmp_path):
+    """One layer of attention, weights made so that the query of the last token matches exactly one earlier
+    token's key with a large score: with that token just inside the last token's chunk the logits follow its
+    value, one position outside they do not; the engine agrees with the plain model in both, in a prompt and
+    when the last token is decoded alone."""
+    from fidatar_configs import attention, config, rot
+
+    chunk, n = 20, 58                      # the last token, at position 57, sees 40..57
+    cfg = config(16, 32, 1e-6, [attention(1, 1, 16, 16, 6.0, chunk=chunk)], alpha=1.0, softcap=50.0)
+    w = make_weights(cfg, 9)
+    # queries and keys read the token's identity: token 1 asks, token 2 answers, the others score about 0
+    emb = torch.zeros(16, 32)
+    emb[:, 8:] = 0.05 * torch.randn(16, 24, generator=torch.Generator().manual_seed(1))
+    emb[1, 0], emb[2, 1], emb[2, 2] = 4.0, 4.0, 4.0
+    w["embed"] = emb
+    for nme in ("q", "k", "v"):
+        w[f"l0.mix.{nme}"] = torch.zeros(16, 32)
+        w[f"l0.mix.{nme}.b"] = torch.zeros(16)
+    w["l0.mix.q"][0, 0] = 1.0              # q = e0 for token 1
+    w["l0.mix.k"][0, 1] = 1.0              # k = e0 for token 2
+    w["l0.mix.v"][:, 2] = torch.linspace(-1, 1, 16)        # only token 2 carries a value worth reading
+    w["l0.mix.q.norm"] = torch.ones(16)
+    w["l0.mix.k.norm"] = torch.ones(16)
+    w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    mdir = str(tmp_path / "planted")
+    write_model(mdir, cfg, 0, weights=w)
+    results = {}
+    for where in (40, 39):                 # just inside, just outside
+        toks = [3 + (i % 11) for i in range(n)]
+        toks[where], toks[-1] = 2, 1
+        ref, _ = plain.forward(cfg, w, toks)
+        results[where] = ref[-1]
+        for what, steps in (("whole", h.trace_whole({"a": toks})), ("decode", h.trace_tail_decode({"a": toks}, tail=3)),
+                            ("portions", h.trace_portions({"a": toks}, sizes=(39, 2, 7, 9)))):
+            got, _ = h.replay_in_process(engine(mdir, "float32", kv_cache_tokens=128), steps)
+            compare(cfg, w, {"a": toks}, got, 6e-5, f"planted key at {where} {what}")
+    assert float((results[40] - results[39]).abs().max()) > 0.5         # the key's value reached the logits only from inside
+
+
+def test_long_decoding_and_first_tokens(models):
+    """300 tokens decoded one by one after a two-token prompt (captured steps), beside a request that starts
+    later; positions 0 and 1 are compared too."""
+    cfg, mdir, weights = models["A"]
+    requests = {"a": tokens(cfg, 300, 11), "b": tokens(cfg, 120, 12)}
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(mdir, dtype)
+        steps = [([("a", requests["a"][:2], [0, 1])], [])]
+        for i in range(2, 300):
+            entries = [("a", [requests["a"][i]], [0])]
+            j = i - 100
+            if 0 <= j < 120:
+                entries.append(("b", [requests["b"][j]], [0]))
+            steps.append((entries, [r for r, n in (("a", 299), ("b", 219)) if i == n]))
+        got, forced = h.replay_in_process(eng, steps, record_routing=(dtype == "bfloat16"))
+        compare(cfg, weights, requests, got, TOL[dtype], f"long decoding {dtype}", forced)
+        assert len(eng._graphs) >= 1 and any(g.captured for g in eng._graphs.values())
+
+
+def test_other_page_sizes_and_kernel_choices(models):
+    """Page sizes 8 and 64; in bfloat16 the 64- and 128-wide heads go through the tensor-core attention kernels
+    (single tokens, short portions, portions of 128 tokens and more), other sizes through the general one."""
+    from hi_b200.kernels import ops
+
+    for name, want in (("A", ("paged_attention",)), ("B", ("attention_prefill_tc", "attention_decode", "attention_prefill"))):
+        cfg, mdir, weights = models[name]
+        requests = {"x": tokens(cfg, 333, 14), "y": tokens(cfg, 40, 15)}
+        for page in (8, 64):
+            before = dict(ops.CALLS)
+            eng = engine(mdir, "bfloat16", kv_page_size=page, kv_cache_tokens=1024)
+            for steps in (h.trace_whole(requests), h.trace_tail_decode(requests, tail=8),
+                          h.trace_portions(requests, sizes=(140, 5, 2, 150, 30))):
+                got, forced = h.replay_in_process(eng, steps, record_routing=True)
+                compare(cfg, weights, requests, got, TOL["bfloat16"], f"{name} page {page}", forced)
+            used = {k for k, v in ops.CALLS.items() if v > before.get(k, 0)}
+            if page == 64:
+                assert all(any(k.startswith(w) for k in used) for w in want), (name, sorted(used))
+            assert {"add_rmsnorm", "qkv_post", "mlstm_gates", "mlstm_recurrence", "mlstm_out_norm", "router_plan", "softcap"} <= used
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_greedy_generation_through_the_entry_point(name, models):
+    """hi_b200.generate (scheduler, sampler, launch-ahead) against greedy decoding of the plain model."""
+    import hi_b200
+
+    cfg, mdir, weights = models[name]
+    prompts = [tokens(cfg, n, 40 + n) for n in (9, 1, 30, 17, 5)]
+    model = PlainFidatar(cfg, weights)
+    outs = hi_b200.generate(mdir, prompts, hi_b200.SamplingParams(max_tokens=12, ignore_eos=True), dtype="float32",
+                            kv_page_size=16, max_batch_size=3, kv_cache_tokens=512, max_batched_tokens=24)
+    for prompt, out in zip(prompts, outs):
+        seq = model.new_sequence()
+        logits = model.forward(seq, prompt)[-1]
+        for k, tok in enumerate(out.token_ids):
+            top2 = torch.topk(logits, 2).values
+            if float(top2[0] - top2[1]) > 1e-3 * float(logits.abs().max()):
+                assert tok == int(logits.argmax()), f"prompt of {len(prompt)}: token {k} is {tok}, plain model says {int(logits.argmax())}"
+            logits = model.forward(seq, [tok])[-1]
+        assert len(out.token_ids) == 12
+
+
+def test_trace_replay_as_a_user_runs_it(models, tmp_path):
+    cfg, mdir, weights = models["B"]
+    requests = {"a": tokens(cfg, 80, 21), "b": tokens(cfg, 33, 22), "c": tokens(cfg, 3, 23), "d": tokens(cfg, 50, 24),
+                "e": tokens(cfg, 20, 25)}
+    steps = h.trace_mixed(requests, max_tokens=192, page=64, seed=5, max_live=4)
+    got = h.replay_subprocess(mdir, "float32", steps, max_tokens=192, out_dir=str(tmp_path / "float32"), vocab=cfg["vocab"],
+                              extra=["--max-live", "4"])
+    compare(cfg, weights, requests, got, TOL["float32"], "trace_run float32")
+    # a model without routed experts in bfloat16 (no choice of expert can fall the other way)
+    cfg, mdir, weights = models["C"]
+    requests = {"a": tokens(cfg, 80, 21), "b": tokens(cfg, 33, 22), "c": tokens(cfg, 3, 23)}
+    steps = h.trace_mixed(requests, max_tokens=192, page=64, seed=6, max_live=4)
+    got = h.replay_subprocess(mdir, "bfloat16", steps, max_tokens=192, out_dir=str(tmp_path / "bfloat16"), vocab=cfg["vocab"],
+                              extra=["--max-live", "4"])
+    compare(cfg, weights, requests, got, TOL["bfloat16"], "trace_run bfloat16")
+
+
+def test_command_line_run_and_inspect(models, capsys):
+    """``python -m hi_b200 run``: the next token, the top logits and greedy generation of a Fidatar folder."""
+    import json
+
+    from hi_b200.cli import main
+
+    cfg, mdir, weights = models["D"]
+    prompt = tokens(cfg, 12, 50)
+    assert main(["run", mdir, "--tokens", ",".join(map(str, prompt)), "--max-tokens", "5", "--top-k", "3",
+                 "--dtype", "float32", "--kv-page-size", "16", "--include-logits"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    ref = plain.forward(cfg, weights, prompt)[0][-1]
+    assert report["next_token"] == int(ref.argmax()) and report["logit_count"] == cfg["vocab"]
+    assert float((torch.tensor(report["logits"], dtype=torch.float64) - ref).abs().max()) <= 3e-5 * float(ref.abs().max())
+    assert [t["token_id"] for t in report["top_logits"]] == torch.topk(ref, 3).indices.tolist()
+    assert len(report["generated_tokens"]) == 5 and report["generated_tokens"][0] == report["next_token"]
+    assert main(["inspect", models["A"][1]]) == 0
+    text = capsys.readouterr().out
+    assert "mlstm" in text and "postnorm" in text and "attention" in text
