@@ -969,6 +969,261 @@ def case_delta_recurrence(tokens=2048, heads=16, seqs=1):
         torch.cuda.synchronize()
         print(f"{rows} rows a lane: {a.elapsed_time(b) * 1e3:.1f} us")
 
+# --------------------------------------------------------------------------- Fidatar beside the closest existing models
+def _fidatar_config(width, heads, ff, layers, vocab=32000, chunk=8192):
+    """Layers in turn attention (heads of 128, a quarter as many key heads, chunks of 8,192, half of a head
+    rotating) and matrix memory (heads of 128); the feed-forward is dense on every third layer and otherwise 8
+    experts in 4 groups of which 2 stay open, 2 experts a token, each half the dense size."""
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "mask": {"size": chunk}, "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mem = {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    order = [{"type": "attention" if i % 2 == 0 else "mlstm", "mixer": att if i % 2 == 0 else mem,
+              "mlp": {"kind": "dense", "ff": ff} if i % 3 == 0 else moe} for i in range(layers)]
+    return {"architecture": "Fidatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
+            "postln_alpha": 2.0, "logit_softcap": 30.0, "layers": order}
+
+
+def case_fidatar(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, context=4096):
+    """Prefill (one prompt of ``tokens`` in one step) and decode (``batch`` requests at ``context`` cached tokens,
+    captured steps) throughput of a Fidatar model with random weights beside Vinurax (the closest existing
+    model: attention layers in turn with recurrent ones) and a dense Llama-4-shaped model of equal width, depth
+    and heads; then the new and the extended kernels alone beside their like kernels, with the bytes that must
+    move over the measured copy bandwidth. Markdown on standard output."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+    from hi_b200.kernels import ops
+    from hi_b200.parts.basic import yarn_inverse_frequencies
+
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn, reps=5, flush_l2=True):
+        fn()
+        ts = []
+        for _ in range(reps):
+            if flush_l2:
+                flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    print(f"peaks: {pk['hbm_gbs']:.0f} GB/s copy, {pk['bf16_tflops']:.0f} TFLOP/s bf16 ({pk['source']}); "
+          f"width {width}, {heads} heads of 128, feed-forward {ff}, {layers} layers, bf16, random weights\n")
+    print("| model | prefill tokens/s | ms | decode tokens/s | ms/step | weights GB | launches/decode step |\n|---|---|---|---|---|---|---|")
+    for name, cfg in (("Fidatar", _fidatar_config(width, heads, ff, layers)), ("Vinurax", _vinurax_config(width, heads, ff, layers)),
+                      ("dense Llama-4 shape", _dense_llama_config(width, heads, ff, layers))):
+        eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                                 kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1)
+        vocab = eng.vocab_size
+        weights = sum(2 * int(torch.Size(sp.shape).numel()) for sp in eng.model.tensor_specs() if sp.init != "absent") / 1e9
+        prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+
+        def prefill():
+            eng.step([StepEntry("p", prompt, [tokens - 1])])
+            eng.finish("p")
+        t_pre = timed(prefill, reps=3)
+        for i in range(batch):
+            eng.assume_cached(i, context)
+        toks = torch.randint(0, vocab, (64, batch), generator=g).tolist()
+        turn = [0]
+
+        def decode():
+            eng.step([StepEntry(i, [toks[turn[0] % 64][i]], [0]) for i in range(batch)], borrow=True)
+            turn[0] += 1
+        for _ in range(4):
+            decode()
+        before = ops.LAUNCHES[0]
+        t_dec = timed(decode, reps=9, flush_l2=False)
+        launches = (ops.LAUNCHES[0] - before) // 10
+        print(f"| {name} | {tokens / t_pre * 1e3:,.0f} | {t_pre:.2f} | {batch / t_dec * 1e3:,.0f} | {t_dec:.3f} | {weights:.2f} | {launches} |")
+        del eng
+        torch.cuda.empty_cache()
+    ops.check_tc_status()
+
+    # ---- kernels alone: bytes that must move over the time, against the copy peak
+    bf = torch.bfloat16
+    dg = torch.Generator(device=DEV).manual_seed(0)
+    rnd = lambda *shape, dt=bf: torch.randn(*shape, device=DEV, generator=dg).to(dt)
+    rows = []
+
+    def row(kind, name, ms, nbytes, note=""):
+        rows.append(f"| {kind} | {name} | {ms * 1e3:.1f} | {nbytes / 1e6:.1f} | {nbytes / ms / 1e6:,.0f} | "
+                    f"{nbytes / ms / 1e6 / pk['hbm_gbs']:.2f} | {note} |")
+
+    hd, nkv = heads * 128, max(1, heads // 4)
+    inv, mag = yarn_inverse_frequencies(64, 1e6, {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+    inv = torch.from_numpy(inv).to(DEV)
+    plain_inv = torch.from_numpy(yarn_inverse_frequencies(128, 1e6, None)[0]).to(DEV)
+    for n, seqs, what in ((tokens, 1, "prefill"), (batch, batch, "decode")):
+        x, d1, w = rnd(n, width, dt=torch.float32), rnd(n, width), rnd(width)
+        ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-6, bf, x_scale=2.0, post=True))
+        row(what, "post-norm boundary: scaled stream + delta, RMS norm, stream and its rounding written", ms, n * width * (4 + 2 + 4 + 2))
+        ms = timed(lambda: ops.add_rmsnorm(x, d1, w, 1e-6, bf))
+        row(what, "like: residual add + RMSNorm (pre-norm)", ms, n * width * (4 + 2 + 4 + 2), "the same kernel")
+        up = rnd(n, ff)
+        ms = timed(lambda: ops.relu2(up))
+        row(what, "squared relu", ms, n * ff * 4)
+        gu = rnd(n, 2 * (2 * ff // 3))
+        ms = timed(lambda: ops.swiglu(gu))
+        row(what, "like: SwiGLU", ms, n * (2 * ff // 3) * 6)
+        # encoding of q, k, v and the append
+        pages = n // PAGE + 1
+        pos = torch.arange(n, dtype=torch.int32, device=DEV)
+        sot = torch.zeros(n, dtype=torch.int32, device=DEV)
+        table = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages)
+        qkv = rnd(n, (heads + 2 * nkv) * 128)
+        kp, vp = (torch.zeros(pages, nkv, PAGE, 128, dtype=bf, device=DEV) for _ in range(2))
+        wq, wk = rnd(128, dt=torch.float32), rnd(128, dt=torch.float32)
+        ms = timed(lambda: ops.qkv_post(qkv, heads, nkv, 128, pos, inv, False, True, 1e-6, None, sot, table, kp, vp, PAGE, True,
+                                        q_norm_weight=wq, k_norm_weight=wk, norm_first=True, norm_dim=128, rot_mul=mag))
+        row(what, "q/k/v encoding: weighted norm, then 64 of 128 dims rotate with a magnitude factor; append", ms,
+            n * (heads + 2 * nkv) * 128 * 4)
+        ms = timed(lambda: ops.qkv_post(qkv, heads, nkv, 128, pos, plain_inv, False, True, 1e-6, None, sot, table, kp, vp, PAGE, True))
+        row(what, "like: q/k/v encoding (rotation of all dims, then the weightless norm) and append", ms, n * (heads + 2 * nkv) * 128 * 4)
+        # the matrix memory beside the delta rule
+        state = torch.zeros(seqs, ops.mlstm_state_floats(heads, 128, 128), device=DEV)
+        proj = rnd(n, 4 * hd)
+        z = rnd(n, 2 * heads, dt=torch.float32)
+        bi, bfg = rnd(heads, dt=torch.float32), rnd(heads, dt=torch.float32) + 3
+        cu = torch.arange(0, n + 1, n // seqs, dtype=torch.int32, device=DEV)
+        slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
+        ms = timed(lambda: ops.mlstm_gates(z, bi, bfg, 15.0, state, cu, slots, heads, 128, 128))
+        row(what, "matrix memory: gates, running maximum, keep / take / floor", ms, n * heads * (8 + 12))
+        keep, take, floor = ops.mlstm_gates(z, bi, bfg, 15.0, state, cu, slots, heads, 128, 128)
+        ms = timed(lambda: ops.mlstm_recurrence(proj, 0, hd, 2 * hd, 128 ** -0.5, keep, take, state, cu, slots, heads, 128, 128))
+        flops = n * heads * 128 * 129 * 2 * 3
+        row(what, "matrix memory: recurrence (S and n)", ms, n * (3 * hd * 2 + hd * 4 + heads * 12) + 2 * state.numel() * 4,
+            f"{flops / ms / 1e9:,.1f} TFLOP/s float32 of the recurrence's own arithmetic")
+        o, nq = ops.mlstm_recurrence(proj, 0, hd, 2 * hd, 128 ** -0.5, keep, take, state, cu, slots, heads, 128, 128)
+        wn = rnd(hd)
+        ms = timed(lambda: ops.mlstm_out_norm(o, nq, floor, proj, 3 * hd, wn, 1e-6, bf))
+        row(what, "matrix memory: division, output norm and gate", ms, n * hd * (4 + 2 + 2))
+        C, s_len = 3 * hd, heads * 128 * 128
+        dstate = torch.zeros(seqs, s_len + 3 * C, device=DEV)
+        dproj, taps = rnd(n, C + heads + 128), rnd(C, 4, dt=torch.float32)
+        a_pre, dtb, alog = rnd(n, hd, dt=torch.float32), rnd(hd, dt=torch.float32), rnd(heads, dt=torch.float32)
+        sotd = torch.repeat_interleave(torch.arange(seqs, device=DEV), n // seqs).to(torch.int32)
+        ms = timed(lambda: ops.delta_prep(dproj, 0, C, taps, dstate, s_len, a_pre, dtb, alog, cu, sotd, slots, heads, heads, 128, 128))
+        row(what, "like: delta rule: convolution, unit q/k, beta, decay", ms, n * (C * 2 + hd * 4 + (C + hd + heads) * 4))
+        q, k, v, beta, decay = ops.delta_prep(dproj, 0, C, taps, dstate, s_len, a_pre, dtb, alog, cu, sotd, slots, heads, heads, 128, 128)
+        ms = timed(lambda: ops.delta_recurrence(q, k, v, beta, decay, dstate, cu, slots, heads, heads, 128, 128, single_tokens=seqs == n))
+        row(what, "like: delta rule: recurrence", ms, n * (C + hd + heads + hd) * 4 + 2 * seqs * s_len * 4,
+            f"{n * heads * 128 * 128 * 2 * 3 / ms / 1e9:,.1f} TFLOP/s float32")
+        og, gate, wn1 = rnd(n, hd, dt=torch.float32), rnd(n, hd), rnd(128)
+        ms = timed(lambda: ops.delta_out_norm(og, gate, wn1, 1e-5, 128, bf))
+        row(what, "like: delta rule: output norm and gate", ms, n * hd * (4 + 2 + 2))
+        # routing and the experts
+        xr, wr = rnd(n, width, dt=torch.float32), rnd(8, width)
+        ms = timed(lambda: ops.router_plan(xr, wr, 2, ops.router_groups(4, 2), 1.5))
+        row(what, "router: 8 experts in 4 groups, 2 kept, 2 chosen; plan", ms, n * width * 4 + 8 * width * 2)
+        ms = timed(lambda: ops.router_plan(xr, wr, 2, 0, 1.0))
+        row(what, "like: router without groups; plan", ms, n * width * 4 + 8 * width * 2)
+        ids, scores, plan = ops.router_plan(xr, wr, 2, ops.router_groups(4, 2), 1.5)
+        xe = rnd(n, width)
+        e_ff = ff // 2
+        w_up, w_gate, w_down = rnd(8, e_ff, width), rnd(8, e_ff, width), rnd(8, width, e_ff)
+        ones = torch.ones_like(scores)
+        if n * 2 > 10:
+            def experts_relu2():
+                up_ = ops.moe_down_tc(ops.gather_rows(xe, plan, 2), w_up, plan)
+                return ops.moe_down_tc(ops.relu2(up_, bf), w_down, plan)
+
+            def experts_swiglu():
+                return ops.moe_down_tc(ops.moe_gate_up_tc(xe, plan, 2, w_gate, w_up, scores), w_down, plan)
+        else:
+            def experts_relu2():
+                return ops.moe_down(ops.moe_gate_up(xe, plan, 2, None, w_up, ones, True, "relu2"), w_down, plan, True)
+
+            def experts_swiglu():
+                return ops.moe_down(ops.moe_gate_up(xe, plan, 2, w_gate, w_up, scores, True), w_down, plan, True)
+        touched = min(8, n * 2)
+        ms = timed(experts_relu2)
+        fl = n * 2 * 2 * 2 * width * e_ff
+        row(what, "experts without a gate branch (up, squared relu, down)", ms, touched * 2 * e_ff * width * 2 + n * 2 * (width * 6 + e_ff * 4),
+            f"{fl / ms / 1e9:,.0f} TFLOP/s bf16")
+        ms = timed(experts_swiglu)
+        row(what, "like: experts with gate and up (SwiGLU), down", ms, touched * 3 * e_ff * width * 2 + n * 2 * (width * 6 + e_ff * 4),
+            f"{n * 2 * 3 * 2 * width * e_ff / ms / 1e9:,.0f} TFLOP/s bf16")
+    ops.check_tc_status()
+    # attention with the sink term beside the same kernels without it
+    for n, what in ((tokens, "prefill"), (batch, "decode")):
+        cached = 0 if what == "prefill" else context
+        pages = (cached + n) // PAGE + 2
+        kp, vp = (rnd(pages, nkv, PAGE, 128) for _ in range(2))
+        q = rnd(n, heads, 128)
+        if what == "prefill":
+            pos = torch.arange(n, dtype=torch.int32, device=DEV)
+            table = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages)
+            cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+            for sink in (True, False):
+                ms = timed(lambda: ops.prefill_attention_tc(q, kp, vp, table, cu, pos, 1, n, 8192, 0, 128 ** -0.5, sink=sink))
+                row(what, ("attention over the prompt's own keys, with the sink term" if sink else "like: the same kernel without it"), ms,
+                    n * (heads * 2 + 2 * nkv) * 128 * 2, f"{4 * heads * 128 * n * n / 2 / ms / 1e9:,.0f} TFLOP/s bf16")
+        else:
+            pos = torch.full((n,), cached, dtype=torch.int32, device=DEV)
+            table = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages).repeat(n, 1).contiguous()
+            seq = torch.arange(n, dtype=torch.int32, device=DEV)
+            for sink in (True, False):
+                ms = timed(lambda: ops.decode_attention(q, kp, vp, table, seq, pos, 8192, 0, 128 ** -0.5, cached + 1, sink=sink))
+                row(what, ("attention of single tokens over the cache, with the sink term" if sink else "like: the same kernels without it"), ms,
+                    2 * (cached + 1) * nkv * 128 * 2, "every request reads the same pages here: they come from L2")
+    ops.check_tc_status()
+    print("\n| step | kernel | us | MB that must move | GB/s | of the copy peak | |\n|---|---|---|---|---|---|---|")
+    print("\n".join(rows))
+
+
+def case_fidatar_step(tokens=2048, batch=8, context=4096, width=2048, heads=16, ff=8192, layers=4):
+    """One Fidatar prompt step and three decode steps with every kernel launched on its own (no captured graph):
+    for a launch list under ncu."""
+    import torch
+
+    from hi_b200.engine.core import Engine, StepEntry
+
+    eng = Engine.from_config(_fidatar_config(width, heads, ff, layers), seed=0, dtype="bfloat16", device=DEV, kv_page_size=PAGE,
+                             kv_cache_tokens=batch * (context + 256) + tokens + 256, max_active_requests=batch + 1,
+                             use_cuda_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    for rep in range(2):
+        eng.step([StepEntry("p", torch.randint(0, eng.vocab_size, (tokens,), generator=g).tolist(), [tokens - 1])])
+        eng.finish("p")
+    for i in range(batch):
+        eng.assume_cached(i, context)
+    for _ in range(3):
+        eng.step([StepEntry(i, [int(torch.randint(0, eng.vocab_size, (1,), generator=g))], [0]) for i in range(batch)])
+    torch.cuda.synchronize()
+
+
+def case_mlstm_recurrence(tokens=2048, heads=16, seqs=1, dim=128, vdim=128):
+    """The matrix memory's recurrence alone, each of its register layouts twice: for ncu, and timed."""
+    import torch
+
+    from hi_b200.kernels import ops
+
+    dg = torch.Generator(device=DEV).manual_seed(0)
+    n = tokens * seqs
+    proj = (torch.randn(n, heads * (2 * dim + vdim), device=DEV, generator=dg) * 0.5).to(torch.bfloat16)
+    keep = torch.rand(n, heads, device=DEV) * 0.2 + 0.8
+    take = torch.rand(n, heads, device=DEV)
+    state = torch.zeros(seqs, ops.mlstm_state_floats(heads, dim, vdim), device=DEV)
+    cu = torch.arange(0, n + 1, tokens, dtype=torch.int32, device=DEV)
+    slots = torch.arange(seqs, dtype=torch.int32, device=DEV)
+    for rows in (4, 8, 16, 32):
+        if 32 * rows < dim:
+            continue
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        args = (proj, 0, heads * dim, 2 * heads * dim, dim ** -0.5, keep, take, state, cu, slots, heads, dim, vdim, rows)
+        ops.mlstm_recurrence(*args)
+        a.record()
+        ops.mlstm_recurrence(*args)
+        b.record()
+        torch.cuda.synchronize()
+        print(f"{rows} rows a lane: {a.elapsed_time(b) * 1e3:.1f} us")
+
 
 def _timeline(run, warm, what):
     """Kernel starts and ends of one step from the profiler's activity records (real durations, with
@@ -1043,7 +1298,8 @@ def case_prefill_timeline(tokens=2048, layers=4):
 CASES = {"sweep": case_sweep, "decode_timeline": case_decode_timeline, "prefill_timeline": case_prefill_timeline, "decode_attention": case_decode_attention, "decode_attention_fused": case_decode_attention_fused, "expert_gemv": case_expert_gemv, "expert_tc": case_expert_tc,
          "prefill_attention": case_prefill_attention, "decode_step": case_decode_step, "prefill_step": case_prefill_step,
          "vinurax": case_vinurax, "delta_recurrence": case_delta_recurrence,
-         "vinurax_step": case_vinurax_step}
+         "vinurax_step": case_vinurax_step, "fidatar": case_fidatar, "fidatar_step": case_fidatar_step,
+         "mlstm_recurrence": case_mlstm_recurrence}
 
 
 if __name__ == "__main__":

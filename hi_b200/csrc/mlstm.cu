@@ -29,43 +29,58 @@ mlstm_gates_kernel(const float* __restrict__ z, const float* __restrict__ bias_i
                    float cap, float* __restrict__ state, long long state_stride, long long m_off,
                    const int* __restrict__ cu_seqlens, const int* __restrict__ slots, float* __restrict__ keep,
                    float* __restrict__ take, float* __restrict__ floor_, int heads) {
-  __shared__ float gi[GATE_THREADS], gf[GATE_THREADS], mm[GATE_THREADS + 1];
+  __shared__ float warp_f[GATE_THREADS / 32], warp_i[GATE_THREADS / 32], carry[GATE_THREADS / 32 + 1];
   const int h = blockIdx.x, seq = blockIdx.y;
   const int begin = cu_seqlens[seq], end = cu_seqlens[seq + 1];
   if (begin >= end) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* m_state = state + (size_t)slots[seq] * state_stride + m_off + h;
   const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
   const float inv_cap = 1.f / cap;
-  if (threadIdx.x == 0) mm[0] = *m_state;
+  float m_before_block = *m_state;          // every thread carries the maximum that enters the block of tokens
+  // A token maps the maximum m to max(m + f, i); two tokens in turn map it to max(m + f1 + f2, max(i1 + f2, i2)):
+  // the pairs (F, I) combine associatively, so a block of tokens is scanned in a few steps instead of one by one.
   for (int t0 = begin; t0 < end; t0 += GATE_THREADS) {
     const int t = t0 + threadIdx.x;
-    const int count = min(GATE_THREADS, end - t0);
+    float gi = -INFINITY, gf = 0.f;          // past the end: the identity map
     if (t < end) {
       const float zi = z[(size_t)t * 2 * heads + h] + bi, zf = z[(size_t)t * 2 * heads + heads + h] + bf;
-      const float ci = cap * tanhf(zi * inv_cap), cf = cap * tanhf(zf * inv_cap);
-      gi[threadIdx.x] = ci;
-      gf[threadIdx.x] = fminf(cf, 0.f) - log1pf(expf(-fabsf(cf)));      // log sigmoid
+      const float cf = cap * tanhf(zf * inv_cap);
+      gi = cap * tanhf(zi * inv_cap);
+      gf = fminf(cf, 0.f) - log1pf(expf(-fabsf(cf)));      // log sigmoid
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float m = mm[0];
-      for (int j = 0; j < count; ++j) {
-        m = fmaxf(gf[j] + m, gi[j]);
-        mm[j + 1] = m;
+    float F = gf, I = gi;                    // inclusive scan over the warp's tokens
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float Fp = __shfl_up_sync(0xffffffffu, F, off), Ip = __shfl_up_sync(0xffffffffu, I, off);
+      if (lane >= off) {
+        I = fmaxf(Ip + F, I);
+        F = Fp + F;
       }
     }
+    if (lane == 31) { warp_f[warp] = F; warp_i[warp] = I; }
     __syncthreads();
-    if (t < end) {
-      const float before = mm[threadIdx.x], now = mm[threadIdx.x + 1];
-      keep[(size_t)t * heads + h] = expf(gf[threadIdx.x] + before - now);
-      take[(size_t)t * heads + h] = expf(gi[threadIdx.x] - now);
-      floor_[(size_t)t * heads + h] = expf(-now);
+    if (threadIdx.x == 0) {                  // the maximum that enters each warp's tokens, and the next block's
+      float m = m_before_block;
+      for (int w2 = 0; w2 < GATE_THREADS / 32; ++w2) {
+        carry[w2] = m;
+        m = fmaxf(m + warp_f[w2], warp_i[w2]);
+      }
+      carry[GATE_THREADS / 32] = m;
     }
     __syncthreads();
-    if (threadIdx.x == 0) mm[0] = mm[count];
+    const float now = fmaxf(carry[warp] + F, I);
+    float before = __shfl_up_sync(0xffffffffu, now, 1);
+    if (lane == 0) before = carry[warp];
+    if (t < end) {
+      keep[(size_t)t * heads + h] = expf(gf + before - now);
+      take[(size_t)t * heads + h] = expf(gi - now);
+      floor_[(size_t)t * heads + h] = expf(-now);
+    }
+    m_before_block = carry[GATE_THREADS / 32];
+    __syncthreads();
   }
-  __syncthreads();
-  if (threadIdx.x == 0) *m_state = mm[0];
+  if (threadIdx.x == 0) *m_state = m_before_block;
 }
 
 constexpr int REC_THREADS = 256;
@@ -148,6 +163,143 @@ mlstm_recurrence_kernel(const void* __restrict__ proj, int proj_dtype, long long
   }
 }
 
+// The same recurrence for sizes whose rows are whole 16-byte runs (the usual case): q, k and v of the next
+// REC_AHEAD tokens come into shared memory with cp.async, as they are stored, while the block works on the
+// tokens before them; nothing waits for global memory between tokens. T is the projection's element type.
+constexpr int REC_AHEAD = 32;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_4(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+  v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(REC_THREADS)
+mlstm_recurrence_async_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, float q_scale,
+                              const float* __restrict__ keep, const float* __restrict__ take,
+                              float* __restrict__ state, long long state_stride, const int* __restrict__ cu_seqlens,
+                              const int* __restrict__ slots, float* __restrict__ o, float* __restrict__ nq, int heads,
+                              int dim, int vdim, int L) {
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  const int h = blockIdx.y, seq = blockIdx.z;
+  const int begin = cu_seqlens[seq], end = cu_seqlens[seq + 1];
+  if (begin >= end) return;
+  const int cols = REC_THREADS / L;                 // columns of this block; a block never straddles column vdim
+  const int dim_pad = L * R;
+  const int col0 = blockIdx.x * cols;
+  const int my = threadIdx.x / L, sub = threadIdx.x % L;
+  const int col = col0 + my;
+  const bool live = col <= vdim;
+  const bool has_v = col0 < vdim;                   // else: the block of the column of n
+  // a buffer: q [AHEAD][dim_pad] T, k [AHEAD][dim_pad] T, v [AHEAD][cols] T, keep [AHEAD] float, take [AHEAD] float
+  const size_t qk_bytes = (size_t)REC_AHEAD * dim_pad * sizeof(T);
+  const size_t v_bytes = (size_t)REC_AHEAD * cols * sizeof(T);
+  const size_t buf_bytes = 2 * qk_bytes + v_bytes + 2 * REC_AHEAD * sizeof(float);
+  auto q_of = [&](int b) { return reinterpret_cast<T*>(sm_raw + b * buf_bytes); };
+  auto k_of = [&](int b) { return reinterpret_cast<T*>(sm_raw + b * buf_bytes + qk_bytes); };
+  auto v_of = [&](int b) { return reinterpret_cast<T*>(sm_raw + b * buf_bytes + 2 * qk_bytes); };
+  auto g_of = [&](int b) { return reinterpret_cast<float*>(sm_raw + b * buf_bytes + 2 * qk_bytes + v_bytes); };
+  if (dim_pad > dim) {                              // rows past dim stay zero in both buffers
+    for (int b = 0; b < 2; ++b)
+      for (int i = threadIdx.x; i < REC_AHEAD * (dim_pad - dim); i += REC_THREADS) {
+        const int j = i / (dim_pad - dim), d = dim + i % (dim_pad - dim);
+        q_of(b)[j * dim_pad + d] = hb::from_f32<T>(0.f);
+        k_of(b)[j * dim_pad + d] = hb::from_f32<T>(0.f);
+      }
+  }
+  constexpr int PER16 = 16 / (int)sizeof(T);
+  const int row_runs = dim / PER16, v_runs = cols / PER16;
+  auto issue = [&](int t0, int b) {
+    const int count = min(REC_AHEAD, end - t0);
+    for (int i = threadIdx.x; i < count * row_runs; i += REC_THREADS) {
+      const int j = i / row_runs, r = i - j * row_runs;
+      const T* src = proj + (size_t)(t0 + j) * ld + (size_t)h * dim + r * PER16;
+      cp_async_16(q_of(b) + j * dim_pad + r * PER16, src + q_off);
+      cp_async_16(k_of(b) + j * dim_pad + r * PER16, src + k_off);
+    }
+    if (has_v)
+      for (int i = threadIdx.x; i < count * v_runs; i += REC_THREADS) {
+        const int j = i / v_runs, r = i - j * v_runs;
+        cp_async_16(v_of(b) + j * cols + r * PER16, proj + (size_t)(t0 + j) * ld + v_off + (size_t)h * vdim + col0 + r * PER16);
+      }
+    for (int i = threadIdx.x; i < 2 * count; i += REC_THREADS) {
+      const int j = i >> 1;
+      cp_async_4(g_of(b) + (i & 1) * REC_AHEAD + j, ((i & 1) ? take : keep) + (size_t)(t0 + j) * heads + h);
+    }
+    cp_async_commit();
+  };
+  float* S_col = state + (size_t)slots[seq] * state_stride + ((size_t)h * (vdim + 1) + (live ? col : 0)) * dim;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int d = sub * R + r;
+    S[r] = (live && d < dim) ? S_col[d] : 0.f;
+  }
+  issue(begin, 0);
+  int b = 0;
+  for (int t0 = begin; t0 < end; t0 += REC_AHEAD, b ^= 1) {
+    const int count = min(REC_AHEAD, end - t0);
+    if (t0 + REC_AHEAD < end) {
+      issue(t0 + REC_AHEAD, b ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const T* qb = q_of(b) + sub * R;
+    const T* kb = k_of(b) + sub * R;
+    const T* vb = v_of(b) + my;
+    const float* gb = g_of(b);
+#pragma unroll 2
+    for (int j = 0; j < count; ++j) {
+      const float a = gb[j];
+      const float v = has_v ? hb::to_f32(vb[j * cols]) : (col == vdim ? 1.f : 0.f);
+      const float bv = gb[REC_AHEAD + j] * v;
+      float acc = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        float q4[4], k4[4];
+        load4(qb + j * dim_pad + r, q4);
+        load4(kb + j * dim_pad + r, k4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          S[r + e] = fmaf(bv, k4[e], a * S[r + e]);
+          acc = fmaf(S[r + e], q4[e], acc);
+        }
+      }
+      for (int off = L >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (sub == 0 && live) {
+        if (col < vdim) o[((size_t)(t0 + j) * heads + h) * vdim + col] = acc * q_scale;
+        else nq[(size_t)(t0 + j) * heads + h] = acc * q_scale;
+      }
+    }
+    __syncthreads();              // the buffer is free for the tokens after the next ones
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int d = sub * R + r;
+      if (d < dim) S_col[d] = S[r];
+    }
+  }
+}
+
 // One warp per (token, head): h_j = o_j / (max(|n.q|, floor) + 1e-6); y = h / sqrt(mean h^2 + eps) * w[head, j]
 // * sigmoid(gate[token, head, j]); the gate is a column run of `proj`.
 __global__ void mlstm_out_norm_kernel(const float* __restrict__ o, const float* __restrict__ nq,
@@ -193,7 +345,8 @@ extern "C" int hb_mlstm_gates(const float* z, const float* bias_i, const float* 
   return HB_OK;
 }
 
-// rows_per_lane: 0 = chosen by dim (4 up to 128, 8 up to 256, 16 up to 512, 32 up to 1024), or one of 4, 8, 16, 32
+// rows_per_lane: 0 = chosen by dim (4 up to 32, 8 up to 256, 16 up to 512, 32 up to 1024; measured at 2,048 tokens of
+// 16 heads of 128: 636, 558, 656 and 867 us with 4, 8, 16 and 32 rows), or one of 4, 8, 16, 32
 // (the sums over a column's rows then run in another order: results move by rounding).
 extern "C" int hb_mlstm_recurrence(const void* proj, int proj_dtype, long long ld, int q_off, int k_off, int v_off,
                                    float q_scale, const float* keep, const float* take, float* state,
@@ -205,12 +358,47 @@ extern "C" int hb_mlstm_recurrence(const void* proj, int proj_dtype, long long l
   if (n_seqs == 0) return HB_OK;
   if (dim > 1024 || n_seqs > 65535 || heads > 65535) return HB_ERR_UNSUPPORTED;
   int R = rows_per_lane;
-  if (R == 0) R = dim <= 128 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
+  if (R == 0) R = dim <= 32 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
   if (!(R == 4 || R == 8 || R == 16 || R == 32) || 32 * R < dim) return HB_ERR_BAD_ARG;
   int L = 1;
   while (L * R < dim) L *= 2;
   const int cols_per_block = REC_THREADS / L;
   const dim3 grid((vdim + 1 + cols_per_block - 1) / cols_per_block, heads, n_seqs);
+  {
+    // rows and column runs of whole 16-byte pieces, and no block that holds both values and the column of n:
+    // the kernel that stages the next tokens with cp.async
+    const int el = proj_dtype == HB_DTYPE_F32 ? 4 : 2, per16 = 16 / el;
+    const bool aligned = dim % per16 == 0 && vdim % cols_per_block == 0 && cols_per_block % per16 == 0 && ld % per16 == 0 &&
+                         q_off % per16 == 0 && k_off % per16 == 0 && v_off % per16 == 0 &&
+                         (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
+    const size_t asmem = 2 * ((size_t)REC_AHEAD * (2 * L * R + cols_per_block) * el + 2 * REC_AHEAD * sizeof(float));
+    if (aligned && asmem <= 200 * 1024) {
+#define HB_MLSTM_ASYNC(T, RR)                                                                                       \
+  do {                                                                                                              \
+    if (asmem > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(mlstm_recurrence_async_kernel<T, RR>,                                    \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem);                \
+      if (e != cudaSuccess) return (int)e;                                                                          \
+    }                                                                                                               \
+    mlstm_recurrence_async_kernel<T, RR><<<grid, REC_THREADS, asmem, stream>>>(                                     \
+        (const T*)proj, ld, q_off, k_off, v_off, q_scale, keep, take, state, state_stride, cu_seqlens, slots, o, nq, \
+        heads, dim, vdim, L);                                                                                       \
+  } while (0)
+#define HB_MLSTM_ASYNC_R(T)                                                                                         \
+  do {                                                                                                              \
+    if (R == 4) HB_MLSTM_ASYNC(T, 4);                                                                               \
+    else if (R == 8) HB_MLSTM_ASYNC(T, 8);                                                                          \
+    else if (R == 16) HB_MLSTM_ASYNC(T, 16);                                                                        \
+    else HB_MLSTM_ASYNC(T, 32);                                                                                     \
+  } while (0)
+      if (proj_dtype == HB_DTYPE_F32) HB_MLSTM_ASYNC_R(float);
+      else HB_MLSTM_ASYNC_R(__nv_bfloat16);
+#undef HB_MLSTM_ASYNC_R
+#undef HB_MLSTM_ASYNC
+      HB_LAUNCH_CHECK();
+      return HB_OK;
+    }
+  }
   const size_t smem = (size_t)REC_TOKENS * (2 * L * R + cols_per_block + 2) * sizeof(float);
 #define HB_MLSTM_REC(RR)                                                                                          \
   do {                                                                                                            \

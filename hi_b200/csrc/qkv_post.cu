@@ -38,10 +38,14 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
 // of 16; rot = head_dim in Llama 4); the lanes past them own 16 consecutive elements that pass
 // through (and count in the norm). A block is one token and up to 8 warps of its heads; it
 // computes the token's sines and cosines once.
+// norm_first: the norm of q and k is an RMS norm over the head BEFORE the rotation, with a weight per dim
+// (q_w / k_w, float32 [hd], or null); rot_mul multiplies cos and sin.
 template <typename T>
 __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restrict__ inv_freq,
                                 int rot_pairs, int interleaved, int qk_norm, float qk_eps, int temp_on,
-                                float floor_scale, float attn_scale, const int* __restrict__ positions,
+                                float floor_scale, float attn_scale, const float* __restrict__ q_w,
+                                const float* __restrict__ k_w, int norm_first, float rot_mul,
+                                const int* __restrict__ positions,
                                 const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                                 int table_stride, T* __restrict__ q_out, T* __restrict__ k_pages,
                                 T* __restrict__ v_pages, int page_size, int write_kv, int n_tokens, int nh,
@@ -57,7 +61,12 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
   const int pos = positions[t];
   const int half = rot_pairs;                            // pairs (j, j + half) when not interleaved
   if (inv_freq != nullptr && first_head < nh + nkv) {    // a block of v heads alone rotates nothing
-    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sn_s[j], &cs_s[j]);
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[j], &sn, &cs);
+      sn_s[j] = sn * rot_mul;
+      cs_s[j] = cs * rot_mul;
+    }
   }
   __syncthreads();
   const int kind = head < nh ? 0 : (head < nh + nkv ? 1 : 2);  // q, k, v
@@ -95,6 +104,27 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
       hb::load8(src + j0, a);
       hb::load8(src + half + j0, b);
     }
+  }
+  if (norm_first) {
+    // the squares before the rotation, summed over the head's lanes; then x * rsqrt(mean + eps) * w
+    if (active && kind != 2)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (active && kind != 2 && qk_norm) {
+      const float inv = rsqrtf(ss / (float)hd + qk_eps);
+      const float* w = kind == 0 ? q_w : k_w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int ia = consecutive ? 2 * j0 + 2 * i : j0 + i;
+        const int ib = consecutive ? ia + 1 : half + j0 + i;
+        a[i] *= inv * (w ? w[ia] : 1.f);
+        b[i] *= inv * (w ? w[ib] : 1.f);
+      }
+    }
+    ss = 0.f;
+  }
+  if (active) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if (kind != 2 && inv_freq != nullptr && rotates) {
@@ -110,7 +140,7 @@ __global__ void qkv_post_kernel(const T* __restrict__ qkv, const float* __restri
   for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if (!active) return;
   float mul = 1.f;
-  if (kind != 2 && qk_norm) mul = rsqrtf(ss / (float)hd + qk_eps);
+  if (kind != 2 && qk_norm && !norm_first) mul = rsqrtf(ss / (float)hd + qk_eps);
   if (kind == 0 && temp_on)
     mul *= logf(floorf(((float)pos + 1.f) / floor_scale) + 1.f) * attn_scale + 1.f;
 #pragma unroll
@@ -232,8 +262,8 @@ extern "C" int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, in
   if (norm_dim <= 0) norm_dim = hd;
   if (norm_dim > hd || 2 * rot_pairs > norm_dim) return HB_ERR_BAD_ARG;
   if (n_tokens == 0) return HB_OK;
-  const bool fast = hd % 16 == 0 && hd <= kMaxHeadDim && rot_pairs % 8 == 0 /* whole lanes rotate */ && !norm_first &&
-                    !q_norm_w && !k_norm_w && norm_dim == hd && rot_mul == 1.f;
+  const bool fast = hd % 16 == 0 && hd <= kMaxHeadDim && rot_pairs % 8 == 0 /* whole lanes rotate */ && norm_dim == hd &&
+                    (norm_first || (!q_norm_w && !k_norm_w && rot_mul == 1.f));
   if (!fast) {
     // a norm after a rotation that changes lengths would need the rotated squares; no model asks for it
     if (qk_norm && !norm_first && (rot_mul != 1.f || q_norm_w || k_norm_w)) return HB_ERR_UNSUPPORTED;
@@ -264,12 +294,14 @@ extern "C" int hb_qkv_post(const void* qkv, int dtype, const float* inv_freq, in
   if (dtype == HB_DTYPE_F32)
     qkv_post_kernel<float><<<grid, threads, 0, stream>>>(
         (const float*)qkv, inv_freq, rot_pairs, interleaved, qk_norm, qk_eps, temp_on, floor_scale, attn_scale,
+        q_norm_w, k_norm_w, norm_first, rot_mul,
         positions, seq_of_token, block_table, table_stride, (float*)q_out, (float*)k_pages, (float*)v_pages,
         page_size, write_kv, n_tokens, nh, nkv, hd, lanes_per_head);
   else if (dtype == HB_DTYPE_BF16)
     qkv_post_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)qkv, inv_freq, rot_pairs, interleaved, qk_norm, qk_eps, temp_on, floor_scale,
-        attn_scale, positions, seq_of_token, block_table, table_stride, (__nv_bfloat16*)q_out,
+        attn_scale, q_norm_w, k_norm_w, norm_first, rot_mul, positions, seq_of_token, block_table, table_stride,
+        (__nv_bfloat16*)q_out,
         (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, write_kv, n_tokens, nh, nkv, hd, lanes_per_head);
   else
     return HB_ERR_BAD_ARG;
