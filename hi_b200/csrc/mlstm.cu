@@ -179,14 +179,42 @@ __device__ __forceinline__ void cp_async_4(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
-  const float4 a = *reinterpret_cast<const float4*>(p);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-}
 __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
   const uint2 raw = *reinterpret_cast<const uint2*>(p);
   v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
   v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+
+// R consecutive elements as floats, by the widest loads their size allows (16 bytes where R elements fill them)
+template <int R>
+__device__ __forceinline__ void load_row(const float* p, float (&v)[R]) {
+#pragma unroll
+  for (int r = 0; r < R; r += 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p + r);
+    v[r] = a.x; v[r + 1] = a.y; v[r + 2] = a.z; v[r + 3] = a.w;
+  }
+}
+template <int R>
+__device__ __forceinline__ void load_row(const __nv_bfloat16* p, float (&v)[R]) {
+  if constexpr (R % 8 == 0) {
+#pragma unroll
+    for (int r = 0; r < R; r += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(p + r);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[r + 2 * i] = __uint_as_float(w[i] << 16);
+        v[r + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; r += 4) {
+      float t4[4];
+      load4(p + r, t4);
+      v[r] = t4[0]; v[r + 1] = t4[1]; v[r + 2] = t4[2]; v[r + 3] = t4[3];
+    }
+  }
 }
 
 template <typename T, int R>
@@ -251,6 +279,11 @@ mlstm_recurrence_async_kernel(const T* __restrict__ proj, long long ld, int q_of
     const int d = sub * R + r;
     S[r] = (live && d < dim) ? S_col[d] : 0.f;
   }
+  // lane 0 of a live column writes: a value column into o, the column of n into nq
+  const bool writer = sub == 0 && live;
+  float* out_ptr = col < vdim ? o + ((size_t)begin * heads + h) * vdim + col : nq + (size_t)begin * heads + h;
+  const size_t out_stride = col < vdim ? (size_t)heads * vdim : (size_t)heads;
+  const float fixed_v = col == vdim ? 1.f : 0.f;
   issue(begin, 0);
   int b = 0;
   for (int t0 = begin; t0 < end; t0 += REC_AHEAD, b ^= 1) {
@@ -262,32 +295,29 @@ mlstm_recurrence_async_kernel(const T* __restrict__ proj, long long ld, int q_of
       cp_async_wait<0>();
     }
     __syncthreads();
-    const T* qb = q_of(b) + sub * R;
-    const T* kb = k_of(b) + sub * R;
-    const T* vb = v_of(b) + my;
+    const T* qp = q_of(b) + sub * R;
+    const T* kp = k_of(b) + sub * R;
+    const T* vp = v_of(b) + my;
     const float* gb = g_of(b);
+    float* op = out_ptr + (size_t)(t0 - begin) * out_stride;      // read by writers only
 #pragma unroll 2
-    for (int j = 0; j < count; ++j) {
+    for (int j = 0; j < count; ++j, qp += dim_pad, kp += dim_pad, vp += cols, op += out_stride) {
       const float a = gb[j];
-      const float v = has_v ? hb::to_f32(vb[j * cols]) : (col == vdim ? 1.f : 0.f);
-      const float bv = gb[REC_AHEAD + j] * v;
-      float acc = 0.f;
+      const float bv = gb[REC_AHEAD + j] * (has_v ? hb::to_f32(*vp) : fixed_v);
+      float q8[R], k8[R];
+      load_row<R>(qp, q8);
+      load_row<R>(kp, k8);
+      float acc0 = 0.f, acc1 = 0.f;          // two chains: the sum over a lane's rows is not one long dependency
 #pragma unroll
-      for (int r = 0; r < R; r += 4) {
-        float q4[4], k4[4];
-        load4(qb + j * dim_pad + r, q4);
-        load4(kb + j * dim_pad + r, k4);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          S[r + e] = fmaf(bv, k4[e], a * S[r + e]);
-          acc = fmaf(S[r + e], q4[e], acc);
-        }
+      for (int r = 0; r < R; r += 2) {
+        S[r] = fmaf(bv, k8[r], a * S[r]);
+        S[r + 1] = fmaf(bv, k8[r + 1], a * S[r + 1]);
+        acc0 = fmaf(S[r], q8[r], acc0);
+        acc1 = fmaf(S[r + 1], q8[r + 1], acc1);
       }
+      float acc = acc0 + acc1;
       for (int off = L >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-      if (sub == 0 && live) {
-        if (col < vdim) o[((size_t)(t0 + j) * heads + h) * vdim + col] = acc * q_scale;
-        else nq[(size_t)(t0 + j) * heads + h] = acc * q_scale;
-      }
+      if (writer) *op = acc * q_scale;
     }
     __syncthreads();              // the buffer is free for the tokens after the next ones
   }
