@@ -86,6 +86,8 @@ class CpuReference:
         if not isinstance(mix, AttentionMixer) or not isinstance(layer.norm_mixer, RMSNorm) or \
                 not isinstance(layer.norm_feed_forward, RMSNorm) or layer.spec.arrangement != "prenorm":
             raise ValueError(f"the CPU reference does not know the parts of {layer.spec.prefix}")
+        if mix.hd != mix.dim or mix.vdim != mix.dim or mix.sink or mix.norm_weighted:
+            raise ValueError(f"{layer.spec.prefix}: the CPU reference does not know padded heads, a sink or a weighted q/k norm")
         if layer.norm_mixer.eps != layer.norm_feed_forward.eps:
             raise ValueError(f"{layer.spec.prefix}: the CPU reference takes one eps for both norms of a layer")
         nh, nkv, hd = mix.nh, mix.nkv, mix.hd
