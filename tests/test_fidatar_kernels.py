@@ -286,7 +286,8 @@ def test_group_limited_routing(experts, top, groups, n):
 
 
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 3e-6), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("n,hidden,inter,experts,top", [(3, 64, 32, 8, 2), (70, 64, 48, 6, 3), (300, 128, 64, 16, 3), (9, 50, 10, 5, 5)])
+@pytest.mark.parametrize("n,hidden,inter,experts,top", [(3, 64, 32, 8, 2), (70, 64, 48, 6, 3), (300, 128, 64, 16, 3), (9, 50, 10, 5, 5),
+                                                        (12, 64, 16, 12, 10)])
 def test_experts_without_a_gate_branch(dt, tol, n, hidden, inter, experts, top):
     """W_down max(W_up x, 0)^2, weighted by the scores in the sum: the general kernels (few rows and many) and, in
     bfloat16 with many rows, the tensor-core path of the part."""
@@ -320,9 +321,11 @@ def test_experts_without_a_gate_branch(dt, tol, n, hidden, inter, experts, top):
 
 # --------------------------------------------------------------------------- the matrix memory
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 1e-5), (torch.bfloat16, 4e-2)])
-@pytest.mark.parametrize("heads,dim,vdim,cap,rows", [(2, 16, 24, 8.0, 0), (1, 40, 12, 10.0, 0), (3, 8, 8, 15.0, 0), (2, 136, 20, 12.0, 0),
-                                                     (2, 5, 7, 9.0, 0), (4, 4, 36, 5.0, 0), (2, 48, 48, 12.0, 16), (1, 128, 128, 6.0, 8),
-                                                     (1, 300, 4, 6.0, 0)])
+@pytest.mark.parametrize("heads,dim,vdim,cap,rows", [
+    (2, 16, 24, 8.0, 0), (1, 40, 12, 10.0, 0), (3, 8, 8, 15.0, 0), (2, 136, 20, 12.0, 0), (2, 5, 7, 9.0, 0),
+    (4, 4, 36, 5.0, 0), (2, 48, 48, 12.0, 16), (1, 128, 128, 6.0, 8), (1, 300, 4, 6.0, 0),
+    # the staged kernel with 4 to 32 rows a lane, and a key size with padding rows (96 in 128)
+    (2, 128, 128, 6.0, 0), (2, 64, 64, 9.0, 4), (1, 96, 64, 9.0, 4), (2, 64, 192, 12.0, 16), (1, 256, 64, 12.0, 32)])
 def test_mlstm_mixer_alone(dt, tol, heads, dim, vdim, cap, rows):
     """Three requests in state slots 2, 0, 3, fed in steps of unequal portions down to one token; a long run so
     that the running maximum and the decays matter; the unused slot keeps its noise."""
