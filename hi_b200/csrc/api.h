@@ -61,6 +61,7 @@ int hb_attention_decode_fused(const void* qkv, const float* inv_freq, int rot_pa
                               const int* seq_of_token, const int* positions, void* out, int n_tokens, int nh, int nkv,
                               int hd, int page_size, int chunk, int window, float scale, int split_size,
                               int max_splits, float* part_acc, float* part_ml, int* counters, int* status,
+                              const float* q_norm_w, const float* k_norm_w, int norm_first, float rot_mul, int sink,
                               cudaStream_t stream);
 
 int hb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,

@@ -63,6 +63,12 @@ struct Fuse {
   int* counters;                 // [n_tokens * nkv], zero between launches
   int interleaved, qk_norm, temp_on;
   float qk_eps, floor_scale, attn_scale;
+  // norm_first: the norm of q and k is an RMS norm BEFORE the rotation with a weight per dim (q_w / k_w, float32
+  // [head_dim], or null); rot_mul multiplies cos and sin
+  const float* q_w;
+  const float* k_w;
+  int norm_first;
+  float rot_mul;
 };
 
 // One head of the q/k/v row as qkv_post.cu encodes it: head_dim / 16 neighbouring lanes, each with
@@ -95,6 +101,26 @@ __device__ __forceinline__ void encode_head(const __nv_bfloat16* src, int kind, 
       hb::load8(src + j0, a);
       hb::load8(src + HALF + j0, b);
     }
+  }
+  if (f.norm_first) {
+    if (active && kind != 2)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    for (int o = LPH >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (active && kind != 2 && f.qk_norm) {
+      const float inv = rsqrtf(ss / (float)HD + f.qk_eps);
+      const float* w = kind == 0 ? f.q_w : f.k_w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int ia = consecutive ? 2 * j0 + 2 * i : j0 + i;
+        const int ib = consecutive ? ia + 1 : HALF + j0 + i;
+        a[i] *= inv * (w ? w[ia] : 1.f);
+        b[i] *= inv * (w ? w[ib] : 1.f);
+      }
+    }
+    ss = 0.f;
+  }
+  if (active) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if (kind != 2 && f.inv_freq != nullptr && rotates) {
@@ -108,7 +134,7 @@ __device__ __forceinline__ void encode_head(const __nv_bfloat16* src, int kind, 
   }
   for (int o = LPH >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   float mul = 1.f;
-  if (kind != 2 && f.qk_norm) mul = rsqrtf(ss / (float)HD + f.qk_eps);
+  if (kind != 2 && f.qk_norm && !f.norm_first) mul = rsqrtf(ss / (float)HD + f.qk_eps);
   if (kind == 0 && f.temp_on) mul *= logf(floorf(((float)pos + 1.f) / f.floor_scale) + 1.f) * f.attn_scale + 1.f;
   float lo[8], hi[8];
   if (consecutive) {
@@ -218,7 +244,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if constexpr (FUSED) {
     constexpr int LPH = HD / 16, HPW = 32 / LPH;
     if (f.inv_freq != nullptr)
-      for (int j = tid; j < f.rot_pairs; j += NWARPS * 32) sincosf((float)pos * f.inv_freq[j], &sn_s[j], &cs_s[j]);
+      for (int j = tid; j < f.rot_pairs; j += NWARPS * 32) {
+        float sn, cs;
+        sincosf((float)pos * f.inv_freq[j], &sn, &cs);
+        sn_s[j] = sn * f.rot_mul;
+        cs_s[j] = cs * f.rot_mul;
+      }
     for (int c = tid; c < (ROWS - G) * CHUNKS; c += NWARPS * 32)      // the tile's rows past the group are zeros
       *reinterpret_cast<uint4*>(q_s + (G + c / CHUNKS) * STRIDE + (c % CHUNKS) * 8) = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();                               // sines and cosines; the barriers are initialised
@@ -562,7 +593,8 @@ extern "C" int hb_attention_decode_tma(const void* q, const void* k_pages, const
 
 // The fused form: `qkv` [n_tokens, (nh + 2 nkv) * hd] is the q/k/v projection's output; the kernel
 // encodes q, k and v as hb_qkv_post does (inv_freq [rot_pairs] or null; pairs (j, j + rot_pairs) or
-// (2j, 2j + 1); weightless norm; temperature on q), appends the token's key and value to its page,
+// (2j, 2j + 1); weightless norm after the rotation, or with norm_first the weighted RMS norm before it; rot_mul on
+// cos and sin; temperature on q; sink: one more term of score 0 in the softmax's denominator), appends the token's key and value to its page,
 // attends, and combines its own splits: `counters` holds n_tokens * nkv ints that are zero before
 // the call and zero after it. With `counters` null the splits are left in part_acc / part_ml for
 // hb_attention_merge, as hb_attention_decode_tma leaves them. Same shapes and refusals as hb_attention_decode_tma; every token is
@@ -573,7 +605,8 @@ extern "C" int hb_attention_decode_fused(const void* qkv, const float* inv_freq,
                                          const int* seq_of_token, const int* positions, void* out, int n_tokens,
                                          int nh, int nkv, int hd, int page_size, int chunk, int window, float scale,
                                          int split_size, int max_splits, float* part_acc, float* part_ml,
-                                         int* counters, int* status, cudaStream_t stream) {
+                                         int* counters, int* status, const float* q_norm_w, const float* k_norm_w,
+                                         int norm_first, float rot_mul, int sink, cudaStream_t stream) {
   if (!qkv || !k_pages || !v_pages || !block_table || !seq_of_token || !positions || !out || !status) return HB_ERR_BAD_ARG;
   if (n_tokens < 0 || n_pages <= 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || table_stride <= 0 ||
       chunk < 0 || window < 0 || max_splits < 1 || split_size <= 0 || split_size % TILE != 0)
@@ -588,9 +621,10 @@ extern "C" int hb_attention_decode_fused(const void* qkv, const float* inv_freq,
   if ((long long)n_pages * nkv * page_size > 0x7fffffffLL) return HB_ERR_UNSUPPORTED;
   if (n_tokens == 0) return HB_OK;
   Args a{nullptr, block_table, seq_of_token, positions, (__nv_bfloat16*)out, part_acc, part_ml, status,
-         table_stride, nh, nkv, page_size, chunk, split_size, max_splits, page_size < TILE ? page_size : TILE, scale, 0};
+         table_stride, nh, nkv, page_size, chunk, split_size, max_splits, page_size < TILE ? page_size : TILE, scale, sink};
+  if (!norm_first && (q_norm_w || k_norm_w || rot_mul != 1.f)) return HB_ERR_UNSUPPORTED;   // as hb_qkv_post
   Fuse f{(const __nv_bfloat16*)qkv, inv_freq, rot_pairs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, counters,
-         interleaved, qk_norm, temp_on, qk_eps, floor_scale, attn_scale};
+         interleaved, qk_norm, temp_on, qk_eps, floor_scale, attn_scale, q_norm_w, k_norm_w, norm_first, rot_mul};
   if (hd == 128) return launch<128, true>(k_pages, v_pages, n_pages, n_tokens, a, f, stream);
   if (hd == 64) return launch<64, true>(k_pages, v_pages, n_pages, n_tokens, a, f, stream);
   return HB_ERR_UNSUPPORTED;

@@ -29,7 +29,7 @@ _SIGNATURES = {
     "hb_attention_merge": [P, P, P, I, I, I, I, I, P],
     "hb_attention_decode": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
     "hb_attention_decode_tma": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
-    "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P],
+    "hb_attention_decode_fused": [P, P, I, I, I, F, I, F, F, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P, P, I, F, I, P],
     "hb_attention_prefill": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
     "hb_attention_prefill_tc": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
     "hb_router_topk": [P, I, P, I, I, I, I, I, I, F, P, P, P, P],
@@ -730,12 +730,16 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
                            inv_freq: Optional[torch.Tensor], interleaved: bool, qk_norm: bool, qk_eps: float,
                            temperature: Optional[Tuple[float, float]], seq_of_token: torch.Tensor,
                            block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, chunk: int,
-                           window: int, scale: float, max_context: int, merge_inside: bool = True) -> Optional[torch.Tensor]:
+                           window: int, scale: float, max_context: int, merge_inside: bool = True,
+                           q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
+                           norm_first: bool = False, rot_mul: float = 1.0, sink: bool = False) -> Optional[torch.Tensor]:
     """:func:`qkv_post`, :func:`decode_attention` and the merge of its splits in ONE launch, for a step
     of single decoded tokens: ``qkv`` [N, (nh + 2 nkv) * hd] bfloat16 is the projection's output; the
     kernel encodes q, k and v, appends the token's key and value to its page, attends over the cache
     and combines the splits (the block that finishes last does it). Returns [N, nh, hd], or None
-    where the kernel does not take the shapes (the caller then runs the three kernels)."""
+    where the kernel does not take the shapes (the caller then runs the three kernels). ``q_norm_weight``,
+    ``k_norm_weight``, ``norm_first``, ``rot_mul`` and ``sink`` as in :func:`qkv_post` and :func:`paged_attention`
+    (the norm then runs over the whole head)."""
     _need(qkv, "qkv", torch.bfloat16); _need(k_pages, "k_pages", qkv.dtype); _need(v_pages, "v_pages", qkv.dtype)
     for t, nm in ((block_table, "block_table"), (seq_of_token, "seq_of_token"), (positions, "positions")):
         _need(t, nm, torch.int32)
@@ -745,6 +749,13 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
         raise KernelError("qkv or the cache pages do not match the heads and head_dim")
     if not decode_attention_supported(qkv.dtype, nh, nkv, hd) or n * nkv > min(FUSED_COUNTERS, FUSED_MAX_GROUPS):
         return None
+    if inv_freq is not None and (inv_freq.numel() % 8 or 2 * inv_freq.numel() > hd):
+        return None                       # whole lanes of 8 pairs rotate in this kernel
+    for wt in (q_norm_weight, k_norm_weight):
+        if wt is not None:
+            _need(wt, "norm weight", torch.float32)
+            if wt.numel() != hd:
+                raise KernelError(f"a q/k norm weight needs one number per dim of a head ({hd})")
     rot_pairs = _rot_pairs(inv_freq, hd)
     longest = max(int(max_context), 1)
     if chunk > 0:
@@ -763,14 +774,15 @@ def decode_attention_fused(qkv: torch.Tensor, nh: int, nkv: int, hd: int, positi
         float(asc), _ptr(k_pages), _ptr(v_pages), n_pages, _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
         _ptr(positions), _ptr(out), n, nh, nkv, hd, page_size, int(chunk), int(window), float(scale), split_size, splits,
         _ptr(part_acc), _ptr(part_ml), _ptr(_fused_counter_buffer(qkv.device)) if merge_inside else None,
-        _ptr(_tc_status(qkv.device)), _stream())
+        _ptr(_tc_status(qkv.device)), _ptr(q_norm_weight), _ptr(k_norm_weight), int(norm_first), float(rot_mul), int(sink),
+        _stream())
     if code == _UNSUPPORTED:
         return None
     TC_USED[0] = True
     _check(code, "attention_decode_fused")
     if splits > 1 and not merge_inside:
         _check(lib().hb_attention_merge(_ptr(part_acc), _ptr(part_ml), _ptr(out), _dt(out), n * nh, hd, splits,
-                                        0, _stream()), "attention_merge")
+                                        int(sink), _stream()), "attention_merge")
     return out
 
 

@@ -207,12 +207,14 @@ class AttentionMixer(Part):
         sliding = self.window[1] if self.window and self.window[0] == "sliding" else 0
         rot_mul = float(getattr(self.position, "magnitude", 1.0))
         plain = not (self.norm_weighted or self.sink or self.hd != self.dim or rot_mul != 1.0)
-        if plain and ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
+        if self.hd == self.dim and ctx.max_new == 1 and cache.writes and self.FUSED_DECODE and qkv.dtype == torch.bfloat16:
             # a step of single decoded tokens: encoding, cache append, attention and the merge of its
             # splits in one launch, where the kernel takes the shapes
             o = ops.decode_attention_fused(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,
                                            self.qk_norm_eps, self.temperature, ctx.seq_of_token, block_table,
-                                           cache.k_pages, cache.v_pages, chunk, sliding, self.scale, ctx.max_context)
+                                           cache.k_pages, cache.v_pages, chunk, sliding, self.scale, ctx.max_context,
+                                           q_norm_weight=self.w_qnorm, k_norm_weight=self.w_knorm,
+                                           norm_first=self.norm_weighted, rot_mul=rot_mul, sink=self.sink)
             if o is not None:
                 return linear(o.view(o.shape[0], self.nh * self.hd), self.w_o, bias=self.b_o)
         q = ops.qkv_post(qkv, self.nh, self.nkv, self.hd, positions, inv_freq, interleaved, self.qk_norm,

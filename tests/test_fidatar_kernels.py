@@ -399,3 +399,55 @@ def test_mlstm_gates_kernel():
         assert rel(floor[t], torch.exp(-new)) < 2e-5
         m = new
     assert float((state[1, -heads:].cpu() - m).abs().max()) < 1e-5 and float(state[0].abs().max()) == 0
+
+
+# --------------------------------------------------------------------------- the one-launch decode form
+@pytest.mark.parametrize("nh,nkv,hd,page,chunk,rot_dims,scaling", [(16, 4, 128, 64, 8192, 64, (4.0, 4096, 32.0, 1.0)), (8, 8, 64, 16, 0, 32, None),
+                                                                  (12, 4, 64, 32, 512, 64, (2.0, 64, 8.0, 1.0)), (6, 2, 128, 128, 128, 0, None)])
+def test_fused_decode_form_with_weighted_norm_and_sink(nh, nkv, hd, page, chunk, rot_dims, scaling):
+    """Encoding (weighted norm before a partial rotation with a magnitude factor), append, attention with the
+    sink and the merge of its splits in one launch, against the three kernels that the other tests hold
+    against the plain statement: the appended keys and values are the same bits, the outputs agree to
+    bfloat16 rounding. Requests of very different lengths in one batch; twice on the same buffers."""
+    from hi_b200.kernels import ops
+    from hi_b200.parts.basic import yarn_inverse_frequencies
+
+    starts = [0, 1, 63, 64, 255, 256, 1030, 2500, 8191, 8192, 8200]
+    S = len(starts)
+    total = [s + 1 for s in starts]
+    g = torch.Generator().manual_seed(nh * 7 + hd)
+    n_pages = sum(-(-t // page) for t in total) + 2
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-t // page) for t in total)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    c = 0
+    for s in range(S):
+        for b in range(-(-total[s] // page)):
+            bt[s, b] = perm[c]
+            c += 1
+    bf = torch.bfloat16
+    kp = torch.randn(n_pages, nkv, page, hd, generator=g).to(bf)
+    vp = torch.randn(n_pages, nkv, page, hd, generator=g).to(bf)
+    qkv = dev((torch.randn(S, (nh + 2 * nkv) * hd, generator=g) * 1.5).to(bf))
+    pos, sot, bt = dev(torch.tensor(starts, dtype=torch.int32)), dev(torch.arange(S, dtype=torch.int32)), dev(bt)
+    inv, mag = None, 1.0
+    if rot_dims:
+        table, mag = yarn_inverse_frequencies(rot_dims, 1e5, None if scaling is None else dict(zip(("factor", "original", "fast", "slow"), scaling)))
+        inv = dev(torch.from_numpy(table))
+    wq, wk = dev(1 + 0.4 * torch.randn(hd, generator=g)), dev(1 + 0.4 * torch.randn(hd, generator=g))
+    extra = dict(q_norm_weight=wq, k_norm_weight=wk, norm_first=True, rot_mul=mag)
+    for _round in range(2):
+        k1, v1, k2, v2 = dev(kp), dev(vp), dev(kp), dev(vp)
+        q = ops.qkv_post(qkv, nh, nkv, hd, pos, inv, False, True, 1e-6, None, sot, bt, k1, v1, page, True, norm_dim=hd, **extra)
+        want = ops.decode_attention(q, k1, v1, bt, sot, pos, chunk, 0, hd ** -0.5, max(total), sink=True)
+        got = ops.decode_attention_fused(qkv, nh, nkv, hd, pos, inv, False, True, 1e-6, None, sot, bt, k2, v2, chunk, 0,
+                                         hd ** -0.5, max(total), sink=True, **extra)
+        assert got is not None, "the fused kernel refused shapes it is written for"
+        torch.cuda.synchronize()
+        assert torch.equal(k1, k2) and torch.equal(v1, v2), "the appended keys or values differ"
+        assert rel(got, want.double().cpu()) <= 1e-2
+        no_sink = ops.decode_attention_fused(qkv, nh, nkv, hd, pos, inv, False, True, 1e-6, None, sot, bt, dev(kp), dev(vp), chunk, 0,
+                                             hd ** -0.5, max(total), sink=False, **extra)
+        assert rel(no_sink[:2], want[:2].double().cpu()) > 5e-2          # among one or two keys the sink weighs
+        assert int(ops._fused_counter_buffer(torch.device(DEV)).abs().sum()) == 0, "the counters were not left at zero"
+    ops.check_tc_status()
