@@ -1130,8 +1130,7 @@ def case_fidatar(width=2048, heads=16, ff=8192, layers=6, tokens=2048, batch=8, 
         ones = torch.ones_like(scores)
         if n * 2 > 10:
             def experts_relu2():
-                up_ = ops.moe_down_tc(ops.gather_rows(xe, plan, 2), w_up, plan)
-                return ops.moe_down_tc(ops.relu2(up_, bf), w_down, plan)
+                return ops.moe_down_tc(ops.moe_up_relu2_tc(xe, plan, 2, w_up), w_down, plan)
 
             def experts_swiglu():
                 return ops.moe_down_tc(ops.moe_gate_up_tc(xe, plan, 2, w_gate, w_up, scores), w_down, plan)

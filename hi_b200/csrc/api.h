@@ -101,6 +101,8 @@ int hb_moe_down_tc(const void* act, const void* w_down, const int* offsets, int 
                    int hidden, int inter, float* scratch, long long scratch_floats, int* counters, int n_counters,
                    int* status, cudaStream_t stream);
 long long hb_moe_down_tc_scratch_floats(int sms);
+int hb_moe_up_relu2_tc(const void* xs, const void* w_up, const int* offsets, int experts, void* act, int rows, int inter,
+                       int hidden, int* status, cudaStream_t stream);     // act = bfloat16 max(xs W_up^T, 0)^2
 
 int hb_sample_rows(const float* logits, int rows, int vocab, const float* temperatures, const float* uniforms,
                    int* out, cudaStream_t stream);

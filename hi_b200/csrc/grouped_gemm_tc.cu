@@ -68,6 +68,7 @@ struct Params {
   int experts, n_out, K, rows;
   float* scratch;            // not DUAL: [blocks of the launch][BT][BF] partial tiles of the last round's pieces, or null
   int* counters;             // [blocks of the launch] pieces of each cut tile that have arrived; zero between launches
+  int relu2;                 // not DUAL, whole tiles only: out = bfloat16 max(x W^T, 0)^2 (an expert's up stack without a gate)
 };
 constexpr int MAX_PIECES = 4;    // a tile of the last round is cut into at most this many pieces
 constexpr int MIN_PIECE_KB = 8;  // of at least this many k blocks (512 k elements)
@@ -345,6 +346,18 @@ grouped_gemm_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
           if (c < live) {
             float g[32];
             tc::ld32(lane_base + c, g);
+            if (p.relu2) {
+              uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + (size_t)(tile.row0 + c) * p.n_out + f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {           // 32 lanes: 64 bytes in a row
+                if (c + j < tile.tokens && f_ok) {
+                  const float u = fmaxf(g[j], 0.f);
+                  const __nv_bfloat16 r = __float2bfloat16_rn(u * u);
+                  dst[(size_t)j * p.n_out] = *reinterpret_cast<const uint16_t*>(&r);
+                }
+              }
+              continue;
+            }
             float* dst = reinterpret_cast<float*>(p.out) + (size_t)(tile.row0 + c) * p.n_out + f;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {             // 32 lanes: 128 bytes in a row
@@ -506,6 +519,22 @@ extern "C" int hb_moe_down_tc(const void* act, const void* w_down, const int* of
   Params p{offsets, nullptr, nullptr, y, status, experts, hidden, inter, rows, room ? scratch : nullptr, counters};
   return few ? launch<false, 8, BT_SHORT>(act, w_down, nullptr, p, max_tiles, stream)
              : launch<false, 5, BT_LONG>(act, w_down, nullptr, p, max_tiles, stream);
+}
+
+// an expert's up stack alone with the squared relu: xs [rows, hidden] sorted rows -> act bfloat16 [rows, inter]
+// = max(xs W_up[e]^T, 0)^2 (experts without a gate branch; a score, if any, multiplies the experts' outputs)
+extern "C" int hb_moe_up_relu2_tc(const void* xs, const void* w_up, const int* offsets, int experts, void* act, int rows,
+                                  int inter, int hidden, int* status, cudaStream_t stream) {
+  if (!xs || !w_up || !offsets || !act || !status || rows < 0 || experts <= 0) return HB_ERR_BAD_ARG;
+  if (hidden % 8 != 0 || inter % 8 != 0 || hidden <= 0 || inter <= 0) return HB_ERR_UNSUPPORTED;
+  if (rows == 0) return HB_OK;
+  const bool few = rows <= SHORT_STEP_ROWS;
+  const int bt = few ? BT_SHORT : BT_LONG;
+  const int max_tiles = (rows + bt - 1) / bt + (experts < rows ? experts : rows);
+  if (max_tiles > 65535) return HB_ERR_UNSUPPORTED;
+  Params p{offsets, nullptr, nullptr, act, status, experts, inter, hidden, rows, nullptr, nullptr, 1};
+  return few ? launch<false, 8, BT_SHORT>(xs, w_up, nullptr, p, max_tiles, stream)
+             : launch<false, 5, BT_LONG>(xs, w_up, nullptr, p, max_tiles, stream);
 }
 
 extern "C" long long hb_moe_down_tc_scratch_floats(int sms) { return (long long)sms * BT_LONG * BF; }

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "hb_gather_rows": [P, P, I, P, I, I, P],
     "hb_moe_gate_up_tc": [P, P, P, P, P, I, P, P, I, I, I, P, P],
     "hb_moe_down_tc": [P, P, P, I, P, I, I, I, P, c_longlong, P, I, P, P],
+    "hb_moe_up_relu2_tc": [P, P, P, I, P, I, I, I, P, P],
     "hb_argmax_rows": [P, I, I, I, P, P, P, P, P],
     "hb_ranked_rows": [P, I, I, P, P, P, P, P, P],
     "hb_sample_rows": [P, I, I, P, P, P, P],
@@ -1133,6 +1134,21 @@ def moe_gate_up_tc(x: torch.Tensor, plan: MoePlan, top_k: int, w_gate: torch.Ten
     _check(lib().hb_moe_gate_up_tc(_ptr(xs), _ptr(plan.sorted_entry), _ptr(w_gate), _ptr(w_up), _ptr(plan.offsets),
                                    experts, _ptr(scores), _ptr(act), rows, inter, hidden, _ptr(_tc_status(x.device)),
                                    _stream()), "moe_gate_up_tc")
+    TC_USED[0] = True
+    return act
+
+
+def moe_up_relu2_tc(x: torch.Tensor, plan: MoePlan, top_k: int, w_up: torch.Tensor) -> torch.Tensor:
+    """act[slot] = max(x W_up[e]^T, 0)^2 on tcgen05, bfloat16 [N*k, I]: experts without a gate branch (the rows are
+    gathered into expert order first; the squared relu is the product's epilogue)."""
+    _need(x, "x", torch.bfloat16); _need(w_up, "w_up", torch.bfloat16)
+    experts, inter, h2 = w_up.shape
+    if h2 != x.shape[1]:
+        raise KernelError("expert up weights do not match the hidden size")
+    xs = gather_rows(x, plan, top_k)
+    act = torch.empty((xs.shape[0], inter), dtype=x.dtype, device=x.device)
+    _check(lib().hb_moe_up_relu2_tc(_ptr(xs), _ptr(w_up), _ptr(plan.offsets), experts, _ptr(act), xs.shape[0], inter, h2,
+                                    _ptr(_tc_status(x.device)), _stream()), "moe_up_relu2_tc")
     TC_USED[0] = True
     return act
 

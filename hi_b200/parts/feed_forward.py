@@ -250,10 +250,8 @@ class SigmoidRoutedExperts(Part):
         tc = ops.moe_tc_supported(normed, self.w_up)
         few = n * self.top_k <= (self.FEW_ROWS if tc else 128)
         if not few and tc and self.activation == "relu2":
-            # the up stack alone is a plain grouped product: the kernel of the down projection takes it
-            # (float32 out), the squared relu rounds it to the engine's dtype
-            up = ops.moe_down_tc(ops.gather_rows(normed, plan, self.top_k), self.w_up, plan)
-            y = ops.moe_down_tc(ops.relu2(up, normed.dtype), self.w_down, plan)
+            # the up stack alone is a plain grouped product with the squared relu as its epilogue
+            y = ops.moe_down_tc(ops.moe_up_relu2_tc(normed, plan, self.top_k, self.w_up), self.w_down, plan)
         elif not few and tc:
             # many rows per expert: the grouped products run on tcgen05
             act = ops.moe_gate_up_tc(normed, plan, self.top_k, self.w_gate, self.w_up, scores)
