@@ -18,6 +18,7 @@ int hb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* ro
                    int rows, int hidden, float eps, float x_scale, int post, cudaStream_t stream);
 int hb_swiglu(const void* in, void* out, int dtype, int rows, int inter, cudaStream_t stream);
 int hb_relu2(const void* in, int dtype, void* out, int out_dtype, long long n, cudaStream_t stream);   // max(x, 0)^2
+int hb_convert(const void* in, int dtype, void* out, int out_dtype, long long n, cudaStream_t stream);  // a copy in another dtype
 int hb_softcap(float* x, float cap, long long n, cudaStream_t stream);                     // cap tanh(x / cap), in place
 int hb_moe_combine(const float* y, const int* slot_of_entry, const float* routed_weight, const void* shared,
                    int shared_dtype, float* out,

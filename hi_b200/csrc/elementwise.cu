@@ -338,6 +338,25 @@ extern "C" int hb_relu2(const void* in, int dtype, void* out, int out_dtype, lon
   return HB_OK;
 }
 
+// out = in, elementwise, in another dtype (the stream's rounding for a sub-layer that reads it before any norm)
+__global__ void convert_kernel(const void* __restrict__ in, int dtype, void* __restrict__ out, int out_dtype, size_t n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t groups = n / 4;
+  for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += stride)
+    store4_any(out, out_dtype, g * 4, load4_any(in, dtype, g * 4));
+  for (size_t i = groups * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    store_any(out, out_dtype, i, load_any(in, dtype, i));
+}
+
+extern "C" int hb_convert(const void* in, int dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+  if (!in || !out || n < 0 || !dtype_ok(dtype) || !dtype_ok(out_dtype)) return HB_ERR_BAD_ARG;
+  if (n == 0) return HB_OK;
+  const long long want = (n / 4 + 255) / 256 + 1;
+  convert_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(in, dtype, out, out_dtype, (size_t)n);
+  HB_LAUNCH_CHECK();
+  return HB_OK;
+}
+
 // x <- cap * tanh(x / cap) in place, float32 (a soft limit on the logits)
 __global__ void softcap_kernel(float* __restrict__ x, float cap, float inv_cap, size_t n) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)

@@ -23,6 +23,7 @@ _SIGNATURES = {
     "hb_swiglu": [P, P, I, I, I, P],
     "hb_relu2": [P, I, P, I, c_longlong, P],
     "hb_softcap": [P, F, c_longlong, P],
+    "hb_convert": [P, I, P, I, c_longlong, P],
     "hb_moe_combine": [P, P, P, P, I, P, I, I, I, P],
     "hb_qkv_post": [P, I, P, I, I, I, F, I, F, F, P, P, I, I, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P],
     "hb_paged_attention": [P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P],
@@ -225,6 +226,14 @@ def relu2(x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Ten
     _need(x, "x")
     out = torch.empty_like(x, dtype=out_dtype or x.dtype)
     _check(lib().hb_relu2(_ptr(x), _dt(x), _ptr(out), _dt(out), x.numel(), _stream()), "relu2")
+    return out
+
+
+def convert(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """A copy of ``x`` in ``out_dtype`` (float32 or bfloat16, rounded to nearest even)."""
+    _need(x, "x")
+    out = torch.empty_like(x, dtype=out_dtype)
+    _check(lib().hb_convert(_ptr(x), _dt(x), _ptr(out), _dt(out), x.numel(), _stream()), "convert")
     return out
 
 

@@ -360,7 +360,7 @@ class PostNormBlock(Part):
         # the stream in the engine's dtype, as the block before this one left it
         owner, h = ctx.scratch.get("postnorm_stream", (None, None))
         if owner is not residual:
-            h = residual if residual.dtype == self.env.dtype else residual.to(self.env.dtype)
+            h = residual if residual.dtype == self.env.dtype else ops.convert(residual, self.env.dtype)
         y = layer.mixer.forward(h, ctx, cache_view)
         h = self._boundary(layer.norm_mixer, residual, y)
         if layer.feed_forward is not None:

@@ -76,6 +76,10 @@ def test_embedding_multiplier_soft_cap_and_squared_relu():
         out = ops.embed_gather(dev(table), dev(toks), scale=12.5)
         assert torch.equal(out.cpu(), table.float()[toks.long()] * 12.5)
         assert torch.equal(ops.embed_gather(dev(table), dev(toks)).cpu(), table.float()[toks.long()])
+    for n in (64, 67, 5000):
+        x = torch.randn(n, generator=g)
+        assert torch.equal(ops.convert(dev(x), torch.bfloat16).cpu(), x.to(torch.bfloat16))
+        assert torch.equal(ops.convert(dev(x.to(torch.bfloat16)), torch.float32).cpu(), x.to(torch.bfloat16).float())
     z = torch.randn(5, 77, generator=g) * 40
     got = ops.softcap_(dev(z.clone()), 15.0)
     assert rel(got, plain.soft_cap(z.double(), 15.0)) <= 2e-6
