@@ -93,6 +93,15 @@ FD_E = config(77, 50, 1e-5, [
 ], alpha=2.0, emb_scale=3.0, softcap=12.0)
 
 
+# more choices a token than the norm kernel sums in place (the experts' rows are then summed on their own first);
+# one expert in all; sixteen query heads on one key head
+FD_F = config(70, 32, 1e-5, [
+    mlstm(1, 16, 16, 8.0, mlp=moe(12, 10, 8, scale=0.5, groups=(3, 3))),
+    attention(16, 1, 16, 16, 0.3, chunk=48, rot=rot(16, 10000.0), mlp=moe(1, 1, 24)),
+    attention(34, 2, 16, 16, 0.3, mlp=moe(16, 9, 8, scale=1.5, groups=(4, 3))),
+], alpha=2.0, emb_scale=5.0, softcap=25.0)
+
+
 def peaked(cfg: dict, factor: float) -> dict:
     """The same model with every attention scale multiplied: the softmax then puts nearly all of its
     weight on one key (or on the sink), so a key that is lost, doubled or shifted shows in the logits."""

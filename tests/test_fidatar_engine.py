@@ -8,7 +8,7 @@ import torch
 
 import harness as h
 import plain_fidatar as plain
-from fidatar_configs import FD_A, FD_B, FD_C, FD_D, FD_E, PlainFidatar, make_weights, peaked, write_model
+from fidatar_configs import FD_A, FD_B, FD_C, FD_D, FD_E, FD_F, PlainFidatar, make_weights, peaked, write_model
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -22,7 +22,7 @@ DEV = "cuda:0"
 # There the MEDIAN error of a comparison's positions is held to the tolerance (a fault in a kernel that only
 # bfloat16 takes moves most positions by far more); each such kernel alone is compared sharply in test_fidatar_kernels.
 TOL = {"float32": 6e-5, "bfloat16": 6e-2}
-CONFIGS = {"A": FD_A, "B": FD_B, "C": FD_C, "D": FD_D, "E": FD_E}
+CONFIGS = {"A": FD_A, "B": FD_B, "C": FD_C, "D": FD_D, "E": FD_E, "F": FD_F}
 
 
 @pytest.fixture(scope="module")
@@ -119,7 +119,7 @@ def test_attention_mixer_alone(dt, tol, layer):
 
 
 # --------------------------------------------------------------------------- the model in the engine
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_four_ways_of_cutting(name, dtype, models):
     cfg, mdir, weights = models[name]

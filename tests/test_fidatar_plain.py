@@ -8,9 +8,9 @@ import pytest
 import torch
 
 import plain_fidatar as plain
-from fidatar_configs import FD_A, FD_B, FD_C, FD_D, FD_E, make_weights, peaked
+from fidatar_configs import FD_A, FD_B, FD_C, FD_D, FD_E, FD_F, make_weights, peaked
 
-CONFIGS = {"A": FD_A, "B": FD_B, "C": FD_C, "D": FD_D, "E": FD_E}
+CONFIGS = {"A": FD_A, "B": FD_B, "C": FD_C, "D": FD_D, "E": FD_E, "F": FD_F}
 
 
 def tokens(cfg, n, seed):
