@@ -81,8 +81,8 @@ def test_embedding_multiplier_soft_cap_and_squared_relu():
         assert torch.equal(ops.convert(dev(x), torch.bfloat16).cpu(), x.to(torch.bfloat16))
         assert torch.equal(ops.convert(dev(x.to(torch.bfloat16)), torch.float32).cpu(), x.to(torch.bfloat16).float())
     z = torch.randn(5, 77, generator=g) * 40
-    got = ops.softcap_(dev(z.clone()), 15.0)
-    assert rel(got, plain.soft_cap(z.double(), 15.0)) <= 2e-6
+    got = ops.softcap_(dev(z.clone()), 18.0)
+    assert rel(got, plain.soft_cap(z.double(), 18.0)) <= 2e-6
     for n in (64, 67, 5000):
         x = torch.randn(n, generator=g)
         assert torch.equal(ops.relu2(dev(x)).cpu(), torch.clamp(x, min=0) ** 2)
@@ -158,7 +158,7 @@ def _reference(q, k, v, q_pos, scale, chunk):
 
 @pytest.mark.parametrize("dt,hd,chunk,tol", [
     (torch.float32, 16, 24, 3e-6), (torch.float32, 80, 0, 3e-6), (torch.float32, 64, 1, 3e-6),
-    (torch.bfloat16, 64, 120, 1.5e-2), (torch.bfloat16, 128, 0, 1.5e-2), (torch.bfloat16, 64, 128, 1.5e-2), (torch.bfloat16, 48, 37, 1.5e-2)])
+    (torch.bfloat16, 64, 104, 1.5e-2), (torch.bfloat16, 128, 0, 1.5e-2), (torch.bfloat16, 64, 128, 1.5e-2), (torch.bfloat16, 48, 37, 1.5e-2)])
 def test_sink_softmax_single_tokens(dt, hd, chunk, tol):
     """One decoded token per request at contexts that end just inside, on and just after a chunk's edge and far
     into a long context (splits). The same call without the sink differs: the sink is not a no-op."""
@@ -188,7 +188,7 @@ def test_sink_softmax_single_tokens(dt, hd, chunk, tol):
         assert rel(ops.decode_attention(*args), want) > 10 * tol
 
 
-@pytest.mark.parametrize("hd,chunk,new,start", [(64, 120, 300, 0), (64, 120, 9, 231), (128, 0, 260, 40), (64, 64, 130, 62),
+@pytest.mark.parametrize("hd,chunk,new,start", [(64, 104, 300, 0), (64, 104, 9, 210), (128, 0, 260, 40), (64, 64, 130, 62),
                                                 (128, 200, 2, 199), (64, 0, 140, 700)])
 def test_sink_softmax_portions_bfloat16(hd, chunk, new, start):
     """Portions of a prompt through the mma.sync kernel and, from 128 new tokens, the tcgen05 kernel, with and
@@ -258,7 +258,7 @@ def test_a_far_key_and_the_sink_under_a_peaked_softmax():
 
 
 # --------------------------------------------------------------------------- routing and experts
-@pytest.mark.parametrize("experts,top,groups,n", [(8, 2, (4, 2), 5), (16, 3, (4, 3), 150), (6, 3, (3, 2), 33), (12, 4, (2, 1), 200),
+@pytest.mark.parametrize("experts,top,groups,n", [(8, 2, (4, 2), 5), (16, 5, (4, 2), 150), (6, 3, (3, 2), 33), (12, 4, (2, 1), 200),
                                                   (4, 1, (2, 2), 7), (4, 2, (1, 1), 9), (9, 2, (3, 2), 120), (5, 5, None, 11),
                                                   (64, 6, (8, 4), 40)])
 def test_group_limited_routing(experts, top, groups, n):

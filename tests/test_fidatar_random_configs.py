@@ -37,7 +37,7 @@ def draw(rng: random.Random, large: bool) -> dict:
             dims = rng.choice([d for d in (2, 4, 6, 8, 12, 16, 24, 32, 64, dim) if d <= dim and d % 2 == 0])
             scaling = rng.choice([None, (rng.choice([2.0, 4.0, 8.0]), rng.choice([32, 64, 256]), rng.choice([8.0, 32.0]), rng.choice([0.5, 1.0, 2.0]))])
             r = rng.choice([None, rot(dims, rng.choice([100.0, 10000.0, 1e6]), scaling)])
-            chunk = rng.choice([None, 1, 7, 24, 64, 100, 120, 128, 200])
+            chunk = rng.choice([None, 1, 7, 24, 64, 100, 112, 128, 200])
             layers.append(attention(nh, nkv, dim, vdim, rng.choice([0.5, 1.0, 2.0]) * dim ** -0.5, chunk=chunk, rot=r, mlp=draw_ff(rng, large)))
         else:
             dim = rng.choice([64, 128]) if large else rng.choice([3, 8, 16, 20, 48, 64, 100, 130])
